@@ -1,11 +1,14 @@
 """Typed configurations, part descriptions and the architecture registry."""
-from .specs import (ConfigError, PartSpec, RMSNormSpec, RotaryHalfSpec, NoPositionSpec, GQAAttentionSpec,
-                    SwiGLUSpec, LayerSpec, ScheduleEntry, ModelPlan)
+from .specs import (ConfigError, PartSpec, RMSNormSpec, LayerNormSpec, RotaryHalfSpec, NoPositionSpec, SinusoidAddSpec,
+                    CausalConvAddSpec, GQAAttentionSpec, HeadMixAttentionSpec, MinGRUSpec, SwiGLUSpec, DenseMLPSpec,
+                    LayerSpec, ScheduleEntry, ModelPlan)
 from .registry import (Architecture, register_architecture, known_architectures, architecture,
                        architecture_name_of, config_from_dict, read_config)
 from .qwen2 import Qwen2Config
+from .mebalorn import MebalornConfig
 
-__all__ = ["ConfigError", "PartSpec", "RMSNormSpec", "RotaryHalfSpec", "NoPositionSpec", "GQAAttentionSpec",
-           "SwiGLUSpec", "LayerSpec", "ScheduleEntry", "ModelPlan", "Architecture", "register_architecture",
+__all__ = ["ConfigError", "PartSpec", "RMSNormSpec", "LayerNormSpec", "RotaryHalfSpec", "NoPositionSpec",
+           "SinusoidAddSpec", "CausalConvAddSpec", "GQAAttentionSpec", "HeadMixAttentionSpec", "MinGRUSpec",
+           "SwiGLUSpec", "DenseMLPSpec", "MebalornConfig", "LayerSpec", "ScheduleEntry", "ModelPlan", "Architecture", "register_architecture",
            "known_architectures", "architecture", "architecture_name_of", "config_from_dict", "read_config",
            "Qwen2Config"]

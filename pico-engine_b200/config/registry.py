@@ -48,8 +48,10 @@ def architecture(name: str) -> Architecture:
 
 def architecture_name_of(config_dict: dict) -> str:
     archs = config_dict.get("architectures")
+    if archs is None and isinstance(config_dict.get("architecture"), str):      # the one name as a plain string
+        return config_dict["architecture"]
     if not isinstance(archs, (list, tuple)) or len(archs) != 1 or not isinstance(archs[0], str):
-        raise ConfigError(f'config.json needs "architectures": [one name]; found {archs!r}')
+        raise ConfigError(f'config.json needs "architectures": [one name] or "architecture": "name"; found {archs!r}')
     return archs[0]
 
 

@@ -33,6 +33,15 @@ class RMSNormSpec(PartSpec):
     weight: str                      # tensor name
 
 
+@dataclass(frozen=True)
+class LayerNormSpec(PartSpec):
+    """y = (x - mean) / sqrt(var + eps) * weight + bias, var the mean of the squared deviations."""
+    size: int
+    eps: float
+    weight: str                      # tensor names
+    bias: str
+
+
 # ------------------------------------------------------------------ position encodings
 
 @dataclass(frozen=True)
@@ -46,6 +55,26 @@ class RotaryHalfSpec(PartSpec):
 @dataclass(frozen=True)
 class NoPositionSpec(PartSpec):
     """Queries and keys are used as projected."""
+
+
+@dataclass(frozen=True)
+class SinusoidAddSpec(PartSpec):
+    """A position vector added to the embedding: entry 2i of position p is sin(p * base^(-2i/size)),
+    entry 2i+1 the cosine of the same angle.  It has no tensors."""
+    size: int
+    base: float = 10000.0
+
+
+# ------------------------------------------------------------------ what a sublayer reads
+
+@dataclass(frozen=True)
+class CausalConvAddSpec(PartSpec):
+    """h_t + sum_j w[:, j] * h_(t - taps + 1 + j) on every channel, zeros before a sequence's start
+    (a short causal convolution over time whose result is added to its own input).  ``weight`` names a
+    [size, taps] tensor.  The last ``taps - 1`` inputs of a sequence are state that the cache keeps."""
+    size: int
+    taps: int
+    weight: str
 
 
 # ------------------------------------------------------------------ mixers
@@ -73,6 +102,53 @@ class GQAAttentionSpec(PartSpec):
     o_name: str = "o_proj"
 
 
+@dataclass(frozen=True)
+class HeadMixAttentionSpec(PartSpec):
+    """Softmax attention with grouped key/value heads whose softmax weights are mixed across heads before they
+    meet the values: weight_h(i, j) <- sum_g mix[h, g] * weight_g(i, j); head h applies its mixed weights to
+    the values of its own key/value head.  Options, each absent when its tensor name is None:
+    ``qk_norm`` (RMS norm of every query and key head over ``head_dim`` with one weight vector shared by the
+    heads, eps ``norm_eps``), ``sink`` (one learned logit a head that joins the softmax denominator and has no
+    value), ``head_mix`` ([n_heads, n_heads]; None: the weights stay as they are).  Keys and values may have
+    different head sizes.  ``window`` as in :class:`GQAAttentionSpec`.  Tensor names are ``prefix + name`` for
+    weights and ``prefix + name + bias_suffix`` for biases."""
+    hidden: int
+    n_heads: int
+    n_kv_heads: int
+    head_dim: int
+    v_head_dim: int
+    qkv_bias: bool
+    window: Optional[int]
+    scale: float
+    position: PartSpec
+    prefix: str
+    norm_eps: float = 1e-6
+    q_norm: Optional[str] = None
+    k_norm: Optional[str] = None
+    sink: Optional[str] = None
+    head_mix: Optional[str] = None
+    q_name: str = "q"
+    k_name: str = "k"
+    v_name: str = "v"
+    o_name: str = "o"
+    bias_suffix: str = ".b"
+
+
+@dataclass(frozen=True)
+class MinGRUSpec(PartSpec):
+    """A gated recurrence whose gates read the current token only: z = sigmoid(W_z h + b_z), u = W_x h + b_x,
+    c = u + 1/2 where u >= 0 and sigmoid(u) elsewhere, S_t = (1 - z) S_(t-1) + z c element by element from
+    S = 0, output W_o (S_t * silu(W_g h)).  ``width`` is the size of the state."""
+    hidden: int
+    width: int
+    prefix: str
+    z_name: str = "z"
+    x_name: str = "x"
+    g_name: str = "g"
+    o_name: str = "o"
+    bias_suffix: str = ".b"
+
+
 # ------------------------------------------------------------------ feed-forwards
 
 @dataclass(frozen=True)
@@ -86,6 +162,17 @@ class SwiGLUSpec(PartSpec):
     down_name: str = "down_proj"
 
 
+@dataclass(frozen=True)
+class DenseMLPSpec(PartSpec):
+    """down(act(up(x))), no biases.  ``activation``: "relu2" (the square of relu), "gelu_tanh" or "silu"."""
+    hidden: int
+    intermediate: int
+    prefix: str
+    activation: str = "relu2"
+    up_name: str = "up"
+    down_name: str = "down"
+
+
 # ------------------------------------------------------------------ layers and the model
 
 @dataclass(frozen=True)
@@ -93,7 +180,8 @@ class LayerSpec:
     """One block: which parts it has and how they are arranged around the residual stream.
 
     ``arrangement`` names an entry of ``parts.registry.ARRANGEMENTS``; "pre_norm" is
-    x += mixer(norm(x)); x += ffn(norm(x))  (pico-engine src/pico_engine/model.py:167-237).
+    x += mixer(norm(x)); x += ffn(norm(x))  (pico-engine src/pico_engine/model.py:167-237); "parallel" is
+    x += mixer(norm1(x)) + ffn(norm2(x)), both halves reading the same x.
     Every part is optional: a block without a feed-forward is a mixer-only block (pico-engine's
     recurrent layers are such, src/pico_engine/model.py:389-406), one without a mixer a feed-forward-only
     block, and a half without a norm takes the residual stream as it is.
@@ -103,6 +191,8 @@ class LayerSpec:
     feed_forward: Optional[PartSpec] = None
     feed_forward_norm: Optional[PartSpec] = None
     arrangement: str = "pre_norm"
+    mixer_input: Optional[PartSpec] = None           # applied to norm(x) before the mixer reads it (a CausalConvAddSpec)
+    feed_forward_input: Optional[PartSpec] = None    # the same for the feed-forward
 
 
 @dataclass(frozen=True)
@@ -126,6 +216,8 @@ class ModelPlan:
     max_positions: int
     stop_token_ids: Tuple[int, ...] = ()
     ignorable_tensors: Tuple[str, ...] = field(default_factory=tuple)   # names a checkpoint may carry unused
+    embedding_position: Optional[PartSpec] = None    # added to the embedding by position (a SinusoidAddSpec); None: nothing
+    logit_softcap: Optional[float] = None            # logits <- cap * tanh(logits / cap); None: logits as projected
 
     def validate(self) -> None:
         if not self.layers:

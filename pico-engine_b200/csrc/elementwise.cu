@@ -503,3 +503,73 @@ extern "C" int pe_rope_store(void* qkv, int dtype, int T, int n_q, int n_kv, int
     PE_LAUNCH_CHECK();
     return 0;
 }
+
+// ---------------------------------------------------------------- sinusoidal position vector added to the stream
+// x[t][2i] += sin(pos_t * f_i), x[t][2i + 1] += cos(pos_t * f_i); f [ceil(H / 2)] float32 comes from the host, the angle
+// is the float32 product, sinf and cosf are the accurate ones (no fast-math).
+__global__ void add_sinusoid_kernel(float* x, const int* tok_pos, const float* freq, int H) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const float p = (float)tok_pos[t];
+    float* row = x + (size_t)t * H;
+    for (int i = threadIdx.x; 2 * i < H; i += blockDim.x) {
+        float sn, cs;
+        sincosf(p * freq[i], &sn, &cs);
+        row[2 * i] += sn;
+        if (2 * i + 1 < H) row[2 * i + 1] += cs;
+    }
+}
+
+extern "C" int pe_add_sinusoid(float* x, const int* tok_pos, const float* freq, int T, int H, void* stream) {
+    if (T <= 0) return 0;
+    PE_TRY(pe_launch(add_sinusoid_kernel, T, 256, 0, (cudaStream_t)stream, x, tok_pos, freq, H));
+    PE_LAUNCH_CHECK();
+    return 0;
+}
+
+// ---------------------------------------------------------------- activations of a dense feed-forward
+// kind 0: relu(v)^2; 1: gelu with the tanh formula 0.5 v (1 + tanh(sqrt(2/pi) (v + 0.044715 v^3))); 2: silu.  float32 math.
+template <typename T>
+__global__ void activation_kernel(const T* in, T* out, int kind, size_t total) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x) {
+        const float v = to_f(in[e]);
+        float r;
+        if (kind == 0) { const float p = fmaxf(v, 0.f); r = p * p; }
+        else if (kind == 1) r = 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+        else r = v / (1.0f + expf(-v));
+        out[e] = from_f<T>(r);
+    }
+}
+
+extern "C" int pe_activation(const void* in, void* out, int dtype, int kind, long long total, void* stream) {
+    if (total <= 0) return 0;
+    if (kind < 0 || kind > 2) return PE_ERR_UNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    const long long want = (total + 255) / 256;
+    const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+    if (dtype == PE_F32) PE_TRY(pe_launch(activation_kernel<float>, blocks, 256, 0, s, (const float*)in, (float*)out, kind, (size_t)total));
+    else if (dtype == PE_BF16) PE_TRY(pe_launch(activation_kernel<bf16>, blocks, 256, 0, s, (const bf16*)in, (bf16*)out, kind, (size_t)total));
+    else return PE_ERR_UNSUPPORTED;
+    PE_LAUNCH_CHECK();
+    return 0;
+}
+
+// ---------------------------------------------------------------- soft cap of float32 logits, in place: cap * tanh(l / cap)
+__global__ void softcap_kernel(float* logits, float cap, size_t total) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x)
+        logits[e] = cap * tanhf(logits[e] / cap);
+}
+
+extern "C" int pe_softcap(float* logits, float cap, long long total, void* stream) {
+    if (total <= 0) return 0;
+    const long long want = (total + 255) / 256;
+    const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+    PE_TRY(pe_launch(softcap_kernel, blocks, 256, 0, (cudaStream_t)stream, logits, cap, (size_t)total));
+    PE_LAUNCH_CHECK();
+    return 0;
+}

@@ -1,0 +1,217 @@
+// Layer norm (weight and bias) of the float32 residual stream, the short causal convolution that is added to
+// a sublayer's input, and both of them fused for a block whose two halves read the same stream.
+//
+//   norm:   y = (x - mean) / sqrt(var + eps) * w + b          var = mean of squared deviations, all in float32
+//   conv:   o_t = y_t + sum_j c[:, j] * y_(t - taps + 1 + j)   per channel, zeros before the sequence's start
+//
+// The convolution reaches back taps - 1 tokens.  Inside a step those are earlier rows of the packed tokens of
+// the same sequence; before the step's first token they come from the sequence's state: `state` points at
+// entry 0 of [taps - 1][H] float32 values of the sequence's slot (slots are `state_stride` floats apart), entry
+// k holding the normed row of the token k + 1 places before the step's first token.  A new sequence's state
+// is zero, which is the zero padding.  The state is brought up to date by a kernel of its own (one block per
+// sequence), after the kernel that reads it: a block that reads a slot's old entries and another that writes
+// new ones would otherwise race.  Steps in which every sequence brings one token update the state in the
+// kernel that reads it (each thread rewrites the entries of its own channels after it has read them).
+#include "common.cuh"
+
+#define LN_THREADS 256
+
+extern "C" void pe_set_pdl(int on) { pe_pdl_enabled() = on ? 1 : 0; }     // (this library's own copy of the switch)
+
+// mean and 1/sqrt(var + eps) of one float32 row, two passes (the deviations are squared, not x).
+__device__ __forceinline__ void row_stats(const float* row, int H, float eps, float* scratch, float& mean, float& rstd) {
+    float s = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) s += row[i];
+    mean = block_sum(s, scratch) / (float)H;
+    float v = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) { const float d = row[i] - mean; v = fmaf(d, d, v); }
+    rstd = 1.0f / sqrtf(block_sum(v, scratch) / (float)H + eps);
+}
+
+// ---------------------------------------------------------------- layer norm alone
+template <typename TO>
+__global__ void __launch_bounds__(LN_THREADS) layernorm_kernel(const float* x, const int* rows_index, const void* w, int w_dtype,
+                                                               const void* b, int b_dtype, float eps, TO* out, int H) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float scratch[33];
+    const int r = blockIdx.x;
+    const float* row = x + (size_t)(rows_index ? rows_index[r] : r) * H;
+    float mean, rstd;
+    row_stats(row, H, eps, scratch, mean, rstd);
+    TO* o = out + (size_t)r * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x)
+        o[i] = from_f<TO>((row[i] - mean) * rstd * load_as_f(w, w_dtype, i) + load_as_f(b, b_dtype, i));
+}
+
+extern "C" int pe_layernorm(const float* x, const int* rows_index, const void* w, int w_dtype, const void* b, int b_dtype,
+                            float eps, void* out, int out_dtype, int rows, int H, void* stream) {
+    if (rows <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (out_dtype == PE_F32) PE_TRY(pe_launch(layernorm_kernel<float>, rows, LN_THREADS, 0, s, x, rows_index, w, w_dtype, b, b_dtype, eps, (float*)out, H));
+    else if (out_dtype == PE_BF16) PE_TRY(pe_launch(layernorm_kernel<bf16>, rows, LN_THREADS, 0, s, x, rows_index, w, w_dtype, b, b_dtype, eps, (bf16*)out, H));
+    else return PE_ERR_UNSUPPORTED;
+    PE_LAUNCH_CHECK();
+    return 0;
+}
+
+// ---------------------------------------------------------------- the convolution alone (on float32 normed rows)
+// y [T, H] float32.  Thread per (token, channel).
+template <typename TO>
+__global__ void causal_conv_add_kernel(const float* y, const void* c, int c_dtype, const float* state, long long state_stride,
+                                       const int* tok_row, const int* row_first, const int* slots, TO* out, int T, int H, int taps) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= (size_t)T * H) return;
+    const int t = (int)(e / H), ch = (int)(e % H);
+    const int b = tok_row[t], i = t - row_first[b];
+    const float* st = state + (size_t)slots[b] * state_stride;
+    float acc = y[e];
+    for (int j = 0; j < taps; ++j) {
+        const int back = taps - 1 - j;                       // 0: the token itself
+        const float v = back <= i ? y[(size_t)(t - back) * H + ch] : st[(size_t)(back - i - 1) * H + ch];
+        acc = fmaf(load_as_f(c, c_dtype, (size_t)ch * taps + j), v, acc);
+    }
+    out[e] = from_f<TO>(acc);
+}
+
+extern "C" int pe_causal_conv_add(const float* y, const void* c, int c_dtype, const float* state, long long state_stride,
+                                  const int* tok_row, const int* row_first, const int* slots, void* out, int out_dtype,
+                                  int T, int H, int taps, void* stream) {
+    if (T <= 0) return 0;
+    if (taps < 1) return PE_ERR_UNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t total = (size_t)T * H;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    if (out_dtype == PE_F32) PE_TRY(pe_launch(causal_conv_add_kernel<float>, blocks, 256, 0, s, y, c, c_dtype, state, state_stride, tok_row, row_first, slots, (float*)out, T, H, taps));
+    else if (out_dtype == PE_BF16) PE_TRY(pe_launch(causal_conv_add_kernel<bf16>, blocks, 256, 0, s, y, c, c_dtype, state, state_stride, tok_row, row_first, slots, (bf16*)out, T, H, taps));
+    else return PE_ERR_UNSUPPORTED;
+    PE_LAUNCH_CHECK();
+    return 0;
+}
+
+// New state of every sequence of the step from the normed rows y: entry k <- the row of the step's token
+// n - 1 - k, or, where the step brought fewer tokens, the old entry k - n.  Entries are rewritten from the oldest
+// to the newest, so an old entry is read before it is overwritten.  Block per sequence, thread per channel.
+__global__ void conv_state_update_kernel(const float* y, float* state, long long state_stride, const int* row_first,
+                                         const int* row_lens, const int* slots, int H, int taps) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int b = blockIdx.x;
+    const int n = row_lens[b], first = row_first[b];
+    float* st = state + (size_t)slots[b] * state_stride;
+    for (int ch = blockIdx.y * blockDim.x + threadIdx.x; ch < H; ch += gridDim.y * blockDim.x)
+        for (int k = taps - 2; k >= 0; --k)
+            st[(size_t)k * H + ch] = k < n ? y[(size_t)(first + n - 1 - k) * H + ch] : st[(size_t)(k - n) * H + ch];
+}
+
+extern "C" int pe_conv_state_update(const float* y, float* state, long long state_stride, const int* row_first,
+                                    const int* row_lens, const int* slots, int B, int H, int taps, void* stream) {
+    if (B <= 0 || taps <= 1) return 0;
+    PE_TRY(pe_launch(conv_state_update_kernel, dim3(B, (H + 255) / 256), 256, 0, (cudaStream_t)stream, y, state, state_stride,
+                     row_first, row_lens, slots, H, taps));
+    PE_LAUNCH_CHECK();
+    return 0;
+}
+
+// ---------------------------------------------------------------- both norms and both convolutions of a parallel block
+// One block per token.  The two norms of a parallel block read the same row, so its mean and variance are
+// computed once; the rows of the taps - 1 tokens before it are normed again here (they come from L2) rather
+// than written out in float32 and read back.  Half 2 is skipped when out2 is null.
+#define LC_MAX_TAPS 8
+
+struct NormConvHalf {
+    const void* w; const void* b; const void* c;     // norm weight, norm bias, convolution taps [H, taps]
+    int w_dtype, b_dtype, c_dtype;
+    float* state;                                     // entry 0 of this half's state in slot 0
+    void* out;
+};
+
+template <typename TO>
+__global__ void __launch_bounds__(LN_THREADS) dual_layernorm_conv_kernel(
+    const float* x, NormConvHalf h1, NormConvHalf h2, long long state_stride, const int* tok_row, const int* row_first,
+    const int* slots, float eps, int H, int taps, int update_state) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float scratch[33];
+    const int t = blockIdx.x;
+    const int b = tok_row[t], i = t - row_first[b];
+    const int inside = min(i, taps - 1);                 // how many of the earlier tokens are rows of this step
+    float mean[LC_MAX_TAPS], rstd[LC_MAX_TAPS];
+    for (int back = 0; back <= inside; ++back)
+        row_stats(x + (size_t)(t - back) * H, H, eps, scratch, mean[back], rstd[back]);
+    const size_t slot_off = (size_t)slots[b] * state_stride;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const NormConvHalf& hh = half ? h2 : h1;
+        if (hh.out == nullptr) continue;
+        float* st = hh.state + slot_off;
+        TO* o = (TO*)hh.out + (size_t)t * H;
+        for (int ch = threadIdx.x; ch < H; ch += blockDim.x) {
+            const float w = load_as_f(hh.w, hh.w_dtype, ch), bb = load_as_f(hh.b, hh.b_dtype, ch);
+            const float own = (x[(size_t)t * H + ch] - mean[0]) * rstd[0] * w + bb;
+            float acc = own;
+            for (int j = 0; j < taps; ++j) {
+                const int back = taps - 1 - j;
+                float v;
+                if (back == 0) v = own;
+                else if (back <= inside) v = (x[(size_t)(t - back) * H + ch] - mean[back]) * rstd[back] * w + bb;
+                else v = st[(size_t)(back - i - 1) * H + ch];
+                acc = fmaf(load_as_f(hh.c, hh.c_dtype, (size_t)ch * taps + j), v, acc);
+            }
+            o[ch] = from_f<TO>(acc);
+            if (update_state) {                          // the sequence brings this one token: shift its entries, newest first
+                for (int k = taps - 2; k > 0; --k) st[(size_t)k * H + ch] = st[(size_t)(k - 1) * H + ch];
+                if (taps > 1) st[ch] = own;
+            }
+        }
+    }
+}
+
+// The state after a step that brought several tokens to some sequence: block per sequence.
+__global__ void __launch_bounds__(LN_THREADS) dual_layernorm_state_kernel(
+    const float* x, NormConvHalf h1, NormConvHalf h2, long long state_stride, const int* row_first, const int* row_lens,
+    const int* slots, float eps, int H, int taps) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float scratch[33];
+    const int b = blockIdx.x;
+    const int n = row_lens[b], first = row_first[b];
+    const size_t slot_off = (size_t)slots[b] * state_stride;
+    for (int k = taps - 2; k >= 0; --k) {
+        float mean = 0.f, rstd = 0.f;
+        const float* row = x + (size_t)(first + n - 1 - k) * H;
+        if (k < n) row_stats(row, H, eps, scratch, mean, rstd);
+        for (int half = 0; half < 2; ++half) {
+            const NormConvHalf& hh = half ? h2 : h1;
+            if (hh.out == nullptr) continue;
+            float* st = hh.state + slot_off;
+            for (int ch = threadIdx.x; ch < H; ch += blockDim.x)
+                st[(size_t)k * H + ch] = k < n ? (row[ch] - mean) * rstd * load_as_f(hh.w, hh.w_dtype, ch) + load_as_f(hh.b, hh.b_dtype, ch)
+                                               : st[(size_t)(k - n) * H + ch];
+        }
+    }
+}
+
+extern "C" int pe_dual_layernorm_conv(const float* x, const void* w1, int w1_dtype, const void* b1, int b1_dtype, const void* c1,
+                                      int c1_dtype, float* state1, void* out1, const void* w2, int w2_dtype, const void* b2,
+                                      int b2_dtype, const void* c2, int c2_dtype, float* state2, void* out2, int out_dtype,
+                                      long long state_stride, const int* tok_row, const int* row_first, const int* row_lens,
+                                      const int* slots, float eps, int T, int B, int H, int taps, int one_token_each, void* stream) {
+    if (T <= 0) return 0;
+    if (taps < 1 || taps > LC_MAX_TAPS || out1 == nullptr) return PE_ERR_UNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    NormConvHalf h1 = {w1, b1, c1, w1_dtype, b1_dtype, c1_dtype, state1, out1};
+    NormConvHalf h2 = {w2, b2, c2, w2_dtype, b2_dtype, c2_dtype, state2, out2};
+    const int inline_update = one_token_each ? 1 : 0;
+    if (out_dtype == PE_F32) PE_TRY(pe_launch(dual_layernorm_conv_kernel<float>, T, LN_THREADS, 0, s, x, h1, h2, state_stride, tok_row, row_first, slots, eps, H, taps, inline_update));
+    else if (out_dtype == PE_BF16) PE_TRY(pe_launch(dual_layernorm_conv_kernel<bf16>, T, LN_THREADS, 0, s, x, h1, h2, state_stride, tok_row, row_first, slots, eps, H, taps, inline_update));
+    else return PE_ERR_UNSUPPORTED;
+    PE_LAUNCH_CHECK();
+    if (!inline_update && taps > 1) {
+        PE_TRY(pe_launch(dual_layernorm_state_kernel, B, LN_THREADS, 0, s, x, h1, h2, state_stride, row_first, row_lens, slots, eps, H, taps));
+        PE_LAUNCH_CHECK();
+    }
+    return 0;
+}

@@ -9,7 +9,7 @@ from typing import Optional
 
 import torch
 
-from .library import DTYPE_CODE, KernelError, check, core, extras, stream_ptr
+from .library import DTYPE_CODE, KernelError, check, core, extras, mixers, stream_ptr
 
 PAGE = 64     # tokens per cache page; PE_PAGE in csrc/common.cuh
 
@@ -647,3 +647,198 @@ def gemm_qkv_rope_store(a: torch.Tensor, w_qkv: torch.Tensor, b_qkv: Optional[to
                                       1 if store else 0, ORIENTATION[orientation], status_ptr(a.device), stream_ptr()),
           "gemm_qkv_rope_store")
     return q
+
+
+# ---------------------------------------------------------------------------- pointwise kernels of other designs
+
+def add_sinusoid(x: torch.Tensor, tok_pos: torch.Tensor, freq: torch.Tensor) -> torch.Tensor:
+    """x[t, 2i] += sin(pos_t * freq_i), x[t, 2i + 1] += cos(pos_t * freq_i) on the float32 stream, in place."""
+    T, H = x.shape
+    _need(x, "x", torch.float32); _need(tok_pos, "tok_pos", torch.int32, (T,)); _need(freq, "freq", torch.float32, ((H + 1) // 2,))
+    check(core().pe_add_sinusoid(x.data_ptr(), tok_pos.data_ptr(), freq.data_ptr(), T, H, stream_ptr()), "add_sinusoid")
+    return x
+
+
+ACTIVATIONS = {"relu2": 0, "gelu_tanh": 1, "silu": 2}
+
+
+def activation(h: torch.Tensor, kind: str, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """relu(h)^2, gelu (tanh formula) or silu of every element, computed in float32, stored in h's dtype."""
+    _need(h, "h")
+    if out is None:
+        out = torch.empty_like(h)
+    _need(out, "out", h.dtype, h.shape)
+    check(core().pe_activation(h.data_ptr(), out.data_ptr(), _code(h, "h"), ACTIVATIONS[kind], h.numel(), stream_ptr()), "activation")
+    return out
+
+
+def softcap(logits: torch.Tensor, cap: float) -> torch.Tensor:
+    """logits <- cap * tanh(logits / cap), float32, in place."""
+    _need(logits, "logits", torch.float32)
+    check(core().pe_softcap(logits.data_ptr(), float(cap), logits.numel(), stream_ptr()), "softcap")
+    return logits
+
+
+# ---------------------------------------------------------------------------- layer norm and the input convolution
+
+def layernorm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: float, out_dtype: torch.dtype,
+              rows_index: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Layer norm (weight and bias) of float32 rows [T, H]; with ``rows_index`` (int32 [R]) only of those rows."""
+    T, H = x.shape
+    _need(x, "x", torch.float32); _need(weight, "weight", None, (H,)); _need(bias, "bias", None, (H,))
+    rows = T if rows_index is None else rows_index.shape[0]
+    if rows_index is not None:
+        _need(rows_index, "rows_index", torch.int32)
+    out = torch.empty(rows, H, dtype=out_dtype, device=x.device)
+    check(mixers().pe_layernorm(x.data_ptr(), _ptr(rows_index), weight.data_ptr(), _code(weight, "weight"), bias.data_ptr(),
+                                _code(bias, "bias"), float(eps), out.data_ptr(), _code(out, "out"), rows, H, stream_ptr()), "layernorm")
+    return out
+
+
+def _state_args(state: torch.Tensor, offset: int, elems: int):
+    """Address of element ``offset`` of slot 0 of a float32 state area [slots, elems of all parts] and its row stride."""
+    _need(state, "state", torch.float32)
+    if state.dim() != 2 or offset < 0 or offset + elems > state.shape[1]:
+        raise KernelError(f"a part's state of {elems} numbers at {offset} does not fit rows of {tuple(state.shape)}")
+    return state.data_ptr() + 4 * offset, state.shape[1]
+
+
+def causal_conv_add(y: torch.Tensor, taps_weight: torch.Tensor, state: torch.Tensor, state_offset: int, tok_row: torch.Tensor,
+                    row_first: torch.Tensor, row_lens: torch.Tensor, slots: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """y_t + sum_j c[:, j] y_(t - taps + 1 + j) per channel for float32 rows y [T, H] of packed sequences; the rows before a
+    step's first token come from the sequences' state, which is then brought up to date (entry k: the row k + 1 places
+    before the next step's first token)."""
+    T, H = y.shape
+    taps = taps_weight.shape[1]
+    _need(y, "y", torch.float32); _need(taps_weight, "taps_weight", None, (H, taps))
+    sp, stride = _state_args(state, state_offset, (taps - 1) * H) if taps > 1 else (0, 0)
+    B = slots.shape[0]
+    out = torch.empty(T, H, dtype=out_dtype, device=y.device)
+    lib = mixers()
+    check(lib.pe_causal_conv_add(y.data_ptr(), taps_weight.data_ptr(), _code(taps_weight, "taps_weight"), sp, stride,
+                                 tok_row.data_ptr(), row_first.data_ptr(), slots.data_ptr(), out.data_ptr(), _code(out, "out"),
+                                 T, H, taps, stream_ptr()), "causal_conv_add")
+    if taps > 1:
+        check(lib.pe_conv_state_update(y.data_ptr(), sp, stride, row_first.data_ptr(), row_lens.data_ptr(), slots.data_ptr(),
+                                       B, H, taps, stream_ptr()), "conv_state_update")
+    return out
+
+
+DUAL_NORM_CONV_MAX_TAPS = 8      # LC_MAX_TAPS of csrc/layernorm_conv.cu
+
+
+def dual_layernorm_conv(x: torch.Tensor, halves, eps: float, state: torch.Tensor, tok_row: torch.Tensor, row_first: torch.Tensor,
+                        row_lens: torch.Tensor, slots: torch.Tensor, out_dtype: torch.dtype, one_token_each: bool):
+    """Layer norm and input convolution of one or two sublayers that read the same float32 rows x [T, H], in one pass.
+    ``halves``: one or two tuples (norm weight, norm bias, taps weight [H, taps], state offset); all share eps and taps.
+    Returns one output [T, H] per half.  The sequences' states are brought up to date."""
+    T, H = x.shape
+    _need(x, "x", torch.float32)
+    taps = halves[0][2].shape[1]
+    outs, args = [], []
+    for w, b, c, off in halves:
+        _need(w, "norm weight", None, (H,)); _need(b, "norm bias", None, (H,)); _need(c, "taps weight", None, (H, taps))
+        sp, stride = _state_args(state, off, (taps - 1) * H) if taps > 1 else (0, 0)
+        o = torch.empty(T, H, dtype=out_dtype, device=x.device)
+        outs.append(o)
+        args += [w.data_ptr(), _code(w, "w"), b.data_ptr(), _code(b, "b"), c.data_ptr(), _code(c, "c"), sp, o.data_ptr()]
+    if len(halves) == 1:
+        args += [None, 0, None, 0, None, 0, None, None]
+    check(mixers().pe_dual_layernorm_conv(x.data_ptr(), *args, DTYPE_CODE[out_dtype], stride, tok_row.data_ptr(),
+                                          row_first.data_ptr(), row_lens.data_ptr(), slots.data_ptr(), float(eps), T,
+                                          slots.shape[0], H, taps, 1 if one_token_each else 0, stream_ptr()),
+          "dual_layernorm_conv", 1 if one_token_each or taps == 1 else 2)
+    return outs
+
+
+# ---------------------------------------------------------------------------- the gated recurrence
+
+def mingru(proj: torch.Tensor, state: torch.Tensor, state_offset: int, tok_row: torch.Tensor, row_first: torch.Tensor,
+           row_lens: torch.Tensor, slots: torch.Tensor, chunked: bool) -> torch.Tensor:
+    """S_t = (1 - z) S_(t-1) + z c and y_t = S_t * silu(g) for proj [T, 3W] = z | candidate | gate pre-activations of packed
+    sequences; S comes from and returns to the sequences' float32 state.  ``chunked``: as a segmented scan over chunks of the
+    packed tokens (three launches) instead of token after token."""
+    T, W3 = proj.shape
+    W = W3 // 3
+    _need(proj, "proj")
+    sp, stride = _state_args(state, state_offset, W)
+    B = slots.shape[0]
+    y = torch.empty(T, W, dtype=proj.dtype, device=proj.device)
+    lib = mixers()
+    ws = None
+    if chunked:
+        from .workspace import scratch
+        ws = scratch("mingru.carry", 4 * lib.pe_mingru_scratch_floats(T, B, W), proj.device).data_ptr()
+    check(lib.pe_mingru(proj.data_ptr(), _code(proj, "proj"), sp, stride, tok_row.data_ptr(), row_first.data_ptr(),
+                        row_lens.data_ptr(), slots.data_ptr(), y.data_ptr(), T, B, W, 1 if chunked else 0, ws, stream_ptr()),
+          "mingru", 3 if chunked else 1)
+    return y
+
+
+# ---------------------------------------------------------------------------- attention with mixed heads
+
+def qknorm_store(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, v_head_dim: int, q_weight: Optional[torch.Tensor],
+                 k_weight: Optional[torch.Tensor], eps: float, tok_pos: torch.Tensor, tok_row: torch.Tensor,
+                 k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor], block_table: Optional[torch.Tensor],
+                 table_stride: int) -> None:
+    """RMS norm of every query and key head of qkv [T, H*D + G*D + G*Dv] in place (a weight vector of D for all query heads,
+    one for all key heads; None: that side stays as projected), then keys and values into their cache pages (skipped when
+    ``k_pool`` is None)."""
+    T = qkv.shape[0]
+    _need(qkv, "qkv", None, (T, n_heads * head_dim + n_kv * head_dim + n_kv * v_head_dim))
+    for w, name in ((q_weight, "q_weight"), (k_weight, "k_weight")):
+        if w is not None:
+            _need(w, name, None, (head_dim,))
+    store = k_pool is not None
+    if store:
+        _need(k_pool, "k_pool", qkv.dtype); _need(v_pool, "v_pool", qkv.dtype); _need(block_table, "block_table", torch.int32)
+        if tuple(k_pool.shape[1:]) != (n_kv, PAGE, head_dim) or tuple(v_pool.shape[1:]) != (n_kv, PAGE, v_head_dim):
+            raise KernelError(f"cache pools must be [pages, {n_kv}, {PAGE}, {head_dim}] and [pages, {n_kv}, {PAGE}, {v_head_dim}], "
+                              f"not {tuple(k_pool.shape)} and {tuple(v_pool.shape)}")
+    check(mixers().pe_qknorm_store(qkv.data_ptr(), _code(qkv, "qkv"), T, n_heads, n_kv, head_dim, v_head_dim, _ptr(q_weight),
+                                   0 if q_weight is None else _code(q_weight, "q_weight"), _ptr(k_weight),
+                                   0 if k_weight is None else _code(k_weight, "k_weight"), float(eps), tok_pos.data_ptr(),
+                                   tok_row.data_ptr(), _ptr(k_pool), _ptr(v_pool), _ptr(block_table), table_stride,
+                                   1 if store else 0, stream_ptr()), "qknorm_store")
+
+
+def attention_headmix(q: torch.Tensor, q_stride: int, n_heads: int, n_kv: int, head_dim: int, v_head_dim: int,
+                      k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor, table_stride: int,
+                      tok_pos: torch.Tensor, tok_row: torch.Tensor, window: Optional[int], scale: float,
+                      sink: Optional[torch.Tensor], mix: Optional[torch.Tensor], ctx) -> torch.Tensor:
+    """Attention of the step's tokens over the cache with the softmax weights mixed across heads (``mix`` [H, H]; None: not
+    mixed) and a sink logit a head in the denominator (``sink`` [H]; None: none); [T, H * Dv] in q's dtype."""
+    T = tok_pos.shape[0]
+    _need(q, "q"); _need(k_pool, "k_pool", q.dtype); _need(v_pool, "v_pool", q.dtype)
+    if tuple(k_pool.shape[1:]) != (n_kv, PAGE, head_dim) or tuple(v_pool.shape[1:]) != (n_kv, PAGE, v_head_dim):
+        raise KernelError("cache pools do not have the heads and head sizes of this attention")
+    if sink is not None:
+        _need(sink, "sink", None, (n_heads,))
+    if mix is not None:
+        _need(mix, "mix", None, (n_heads, n_heads))
+    lib = mixers()
+    tiles, n_runs = None, 0
+    if not ctx.one_token_each:
+        tiles = ctx.scratch.get("prefill_tiles")
+        if tiles is None:
+            tiles = ctx.scratch["prefill_tiles"] = prefill_tiles(ctx.lens, ctx.starts, q.device, PREFILL_TILE)
+        n_runs = tiles.shape[0]
+    qt = lib.pe_attention_headmix_tile(n_heads, n_kv, head_dim, v_head_dim, 0 if mix is None else 1, 1 if tiles is None else 16)
+    if qt <= 0:
+        raise KernelError(f"attention with {n_heads} heads of size {head_dim}/{v_head_dim} is not taken: heads x value size "
+                          f"may be 16384 at most")
+    n_tiles = T if tiles is None else n_runs * (PREFILL_TILE // qt)
+    # few tiles with many keys (single tokens with long contexts): the keys are cut into ranges so that the GPU is filled
+    splits = 1
+    if n_tiles < 296:
+        splits = max(1, min(296 // max(n_tiles, 1), (ctx.max_context + 255) // 256, 64))
+    from .workspace import scratch
+    ws = scratch("attention_headmix", 4 * lib.pe_attention_headmix_scratch_floats(n_tiles, splits, qt, n_heads, v_head_dim), q.device)
+    out = torch.empty(T, n_heads * v_head_dim, dtype=q.dtype, device=q.device)
+    check(lib.pe_attention_headmix(q.data_ptr(), q_stride, out.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), _code(q, "q"),
+                                   block_table.data_ptr(), table_stride, tok_pos.data_ptr(), tok_row.data_ptr(), _ptr(tiles),
+                                   n_runs, PREFILL_TILE, T, n_heads, n_kv, head_dim, v_head_dim, window or 0, float(scale),
+                                   _ptr(sink), 0 if sink is None else _code(sink, "sink"), _ptr(mix),
+                                   0 if mix is None else _code(mix, "mix"), qt, splits, ws.data_ptr(), stream_ptr()),
+          "attention_headmix", 2 + (splits > 1))
+    return out

@@ -17,6 +17,9 @@ CORE_SOURCES = ("elementwise.cu", "linear_simt.cu", "attention_generic.cu", "sam
 # this library's small kernels between them still beat (linear_batch.cu: mma.sync with fused prologue and epilogues;
 # gemm_splitk.cu: tcgen05 with K cut over a cluster).
 EXTRA_SOURCES = ("linear_mma.cu", "linear_batch.cu", "gemm_splitk.cu")
+# The kernels of parts that only some designs have (layer norm with the short convolution on a sublayer's input, attention
+# whose weights are mixed across heads, the gated recurrence): compiled when a model with such a part is built.
+MIXER_SOURCES = ("layernorm_conv.cu", "attention_headmix.cu", "gated_recurrence.cu")
 HEAD_DIM_SOURCES = ("attention_decode.cu", "attention_prefill.cu", "attention_prefill_tcgen05.cu")      # compiled per head size
 
 _SIGNATURES = {
@@ -37,6 +40,19 @@ _SIGNATURES = {
     "pe_linear_fused": [P, P, P, I, F, P, P, I, P, I, I, I, I, P, P],
     "pe_norm_gate_up_swiglu": [P, P, I, F, P, P, I, I, I, P, P],
     "pe_norm_qkv_rope_store": [P, P, P, I, F, P, P, I, P, I, I, I, I, I, P, P, P, P, P, P, P, I, I, P, P],
+    "pe_add_sinusoid": [P, P, P, I, I, P],
+    "pe_activation": [P, P, I, I, LL, P],
+    "pe_softcap": [P, F, LL, P],
+}
+
+_MIXER_SIGNATURES = {
+    "pe_layernorm": [P, P, P, I, P, I, F, P, I, I, I, P],
+    "pe_causal_conv_add": [P, P, I, P, LL, P, P, P, P, I, I, I, I, P],
+    "pe_conv_state_update": [P, P, LL, P, P, P, I, I, I, P],
+    "pe_dual_layernorm_conv": [P, P, I, P, I, P, I, P, P, P, I, P, I, P, I, P, P, I, LL, P, P, P, P, F, I, I, I, I, I, P],
+    "pe_mingru": [P, I, P, LL, P, P, P, P, P, I, I, I, I, P, P],
+    "pe_attention_headmix": [P, I, P, P, P, I, P, I, P, P, P, I, I, I, I, I, I, I, I, F, P, I, P, I, I, I, P, P],
+    "pe_qknorm_store": [P, I, I, I, I, I, I, P, I, P, I, F, P, P, P, P, P, I, I, P],
 }
 
 _EXTRA_SIGNATURES = {
@@ -89,6 +105,27 @@ def core() -> ctypes.CDLL:
         lib.pe_sample_scratch_bytes.restype = c_longlong
         _core = lib
     return _core
+
+
+_mixers = None
+
+
+def mixers() -> ctypes.CDLL:
+    """The library of the kernels of layer norm + input convolution, head-mixing attention and the gated recurrence;
+    compiled at the first call."""
+    global _mixers
+    if _mixers is None:
+        lib = build.load("mixers", MIXER_SOURCES)
+        declare(lib, _MIXER_SIGNATURES)
+        lib.pe_set_pdl(0 if os.environ.get("PICO_ENGINE_PDL", "1") == "0" else 1)
+        lib.pe_mingru_scratch_floats.argtypes = [I, I, I]
+        lib.pe_mingru_scratch_floats.restype = c_longlong
+        lib.pe_attention_headmix_tile.argtypes = [I, I, I, I, I, I]
+        lib.pe_attention_headmix_tile.restype = c_int
+        lib.pe_attention_headmix_scratch_floats.argtypes = [I, I, I, I, I]
+        lib.pe_attention_headmix_scratch_floats.restype = c_longlong
+        _mixers = lib
+    return _mixers
 
 
 _extras = None

@@ -2,14 +2,19 @@
 from .base import (ARRANGEMENTS, FEED_FORWARDS, MIXERS, NORMS, POSITIONS, FeedForward, KVView, Mixer, Norm, Part,
                    Position, StepContext, build_part, register_arrangement, register_feed_forward, register_mixer,
                    register_norm, register_position)
-from .norm import RMSNorm
+from .norm import LayerNorm, RMSNorm
 from .position import NoPosition, RotaryHalf
+from .stream_position import SinusoidAdd
+from .input_conv import CausalConvAdd
 from .attention import GQAAttention
-from .feed_forward import SwiGLU
-from .block import Layer, pre_norm
+from .attention_headmix import HeadMixAttention
+from .mingru import MinGRU
+from .feed_forward import DenseMLP, SwiGLU
+from .block import Layer, parallel, pre_norm
 from .model import DecoderModel
 
 __all__ = ["ARRANGEMENTS", "FEED_FORWARDS", "MIXERS", "NORMS", "POSITIONS", "FeedForward", "KVView", "Mixer", "Norm",
            "Part", "Position", "StepContext", "build_part", "register_arrangement", "register_feed_forward",
            "register_mixer", "register_norm", "register_position", "RMSNorm", "NoPosition", "RotaryHalf",
-           "GQAAttention", "SwiGLU", "Layer", "pre_norm", "DecoderModel"]
+           "GQAAttention", "SwiGLU", "Layer", "pre_norm", "DecoderModel", "LayerNorm", "SinusoidAdd", "CausalConvAdd",
+           "HeadMixAttention", "MinGRU", "DenseMLP", "parallel"]

@@ -20,6 +20,13 @@ Mixer         ``cache_needs()``; ``prepare(max_positions)``; ``apply(h, ctx, ent
               owns_cache) -> y``; optionally ``add_to(x, norm, ctx, ...)`` fused
 FeedForward   ``apply(h, ctx) -> y``; optionally ``add_to(x, norm, ctx)`` fused
 Arrangement   ``run(layer, x, ctx, entry, cache_entry, owns_cache)``: updates ``x`` in place
+InputFilter   what stands between a norm and the sublayer that reads it (a short causal convolution): ``state_elems()``;
+              ``apply(y_f32 [T,H], ctx, state, offset, out_dtype) -> [T,H]``, which also brings its state up to date
+StreamPosition  ``prepare(max_positions)``; ``add_to(x, ctx)``: positions added to the embedded stream
+
+State of a layer: ``ctx.state(cache_entry)`` is one float32 area [slot, elems]; the mixer's numbers come first
+(``Mixer.cache_needs().state_elems``), then those of the mixer's input filter, then those of the feed-forward's
+(``Layer.state_offsets``).
 """
 from __future__ import annotations
 
@@ -155,6 +162,23 @@ class Mixer(Part):
         kernels.residual_add(x, self.apply(norm.forward(x, ctx.dtype), ctx, entry, cache_entry, owns_cache).contiguous())
 
 
+class InputFilter(Part):
+    """Applied to the normed rows a sublayer reads; may keep per-sequence state (``state_elems`` float32 numbers)."""
+
+    def state_elems(self) -> int:
+        return 0
+
+    def apply(self, y: torch.Tensor, ctx: StepContext, state: Optional[torch.Tensor], offset: int, out_dtype) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class StreamPosition(Part):
+    """Positions that enter the residual stream once, after the embedding."""
+
+    def add_to(self, x: torch.Tensor, ctx: StepContext) -> None:
+        raise NotImplementedError
+
+
 class FeedForward(Part):
     takes_pending = False
 
@@ -172,6 +196,8 @@ NORMS: Dict[type, type] = {}
 POSITIONS: Dict[type, type] = {}
 MIXERS: Dict[type, type] = {}
 FEED_FORWARDS: Dict[type, type] = {}
+INPUT_FILTERS: Dict[type, type] = {}
+STREAM_POSITIONS: Dict[type, type] = {}
 ARRANGEMENTS: Dict[str, Callable] = {}
 
 
@@ -196,6 +222,14 @@ def register_mixer(spec_class: type):
 
 def register_feed_forward(spec_class: type):
     return _register(FEED_FORWARDS, spec_class)
+
+
+def register_input_filter(spec_class: type):
+    return _register(INPUT_FILTERS, spec_class)
+
+
+def register_stream_position(spec_class: type):
+    return _register(STREAM_POSITIONS, spec_class)
 
 
 def register_arrangement(name: str):

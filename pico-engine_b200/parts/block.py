@@ -3,7 +3,8 @@ absent) and the arrangement that runs them around the residual stream."""
 from __future__ import annotations
 
 from ..config.specs import ConfigError, LayerSpec
-from .base import ARRANGEMENTS, FEED_FORWARDS, MIXERS, NORMS, Norm, build_part, register_arrangement
+from ..cache import CacheNeeds
+from .base import ARRANGEMENTS, FEED_FORWARDS, INPUT_FILTERS, MIXERS, NORMS, Norm, build_part, register_arrangement
 
 
 class PassThrough(Norm):
@@ -29,6 +30,10 @@ class Layer:
         self.feed_forward = build(FEED_FORWARDS, "feed-forward", spec.feed_forward)
         self.mixer_norm = build(NORMS, "norm", spec.mixer_norm) or PassThrough(dtype, device)
         self.feed_forward_norm = build(NORMS, "norm", spec.feed_forward_norm) or PassThrough(dtype, device)
+        self.mixer_input = build(INPUT_FILTERS, "input filter", spec.mixer_input)
+        self.feed_forward_input = build(INPUT_FILTERS, "input filter", spec.feed_forward_input)
+        if (self.mixer_input is not None and self.mixer is None) or (self.feed_forward_input is not None and self.feed_forward is None):
+            raise ConfigError("an input filter needs the sublayer whose input it filters")
         try:
             self._run = ARRANGEMENTS[spec.arrangement]
         except KeyError:
@@ -36,8 +41,24 @@ class Layer:
 
     def parts(self):
         """The parts that are there (a stand-in for an absent norm has no tensors and is left out)."""
-        return tuple(p for p in (self.mixer, self.mixer_norm, self.feed_forward, self.feed_forward_norm)
-                     if p is not None and not isinstance(p, PassThrough))
+        return tuple(p for p in (self.mixer, self.mixer_norm, self.mixer_input, self.feed_forward, self.feed_forward_norm,
+                                 self.feed_forward_input) if p is not None and not isinstance(p, PassThrough))
+
+    def cache_needs(self):
+        """What one execution of the layer keeps in the cache: the mixer's keys, values and state, and behind the
+        mixer's state the states of the input filters (``state_offsets``).  None: nothing."""
+        mixer = self.mixer.cache_needs() if self.mixer is not None else CacheNeeds()
+        extra = sum(f.state_elems() for f in (self.mixer_input, self.feed_forward_input) if f is not None)
+        if not extra:
+            return mixer if self.mixer is not None else None
+        if mixer.state_elems and mixer.state_dtype != "float32":
+            raise ConfigError("input filters keep float32 state; a mixer beside them must keep float32 state too")
+        return CacheNeeds(kv=mixer.kv, state_elems=mixer.state_elems + extra, state_dtype="float32")
+
+    def state_offsets(self):
+        """(offset of the mixer input filter's state, offset of the feed-forward input filter's) in a slot's row."""
+        first = self.mixer.cache_needs().state_elems if self.mixer is not None else 0
+        return first, first + (self.mixer_input.state_elems() if self.mixer_input is not None else 0)
 
     def run(self, x, ctx, entry: int, cache_entry: int, owns_cache: bool) -> None:
         self._run(self, x, ctx, entry, cache_entry, owns_cache)
@@ -54,3 +75,41 @@ def pre_norm(layer: Layer, x, ctx, entry, cache_entry, owns_cache) -> None:
         if not layer.feed_forward.takes_pending:
             ctx.settle(x)
         layer.feed_forward.add_to(x, layer.feed_forward_norm, ctx)
+
+
+@register_arrangement("parallel")
+def parallel(layer: Layer, x, ctx, entry, cache_entry, owns_cache) -> None:
+    """x += mixer(f1(norm1(x))) + feed_forward(f2(norm2(x))): both halves read the same x (f1, f2: the input filters,
+    where the layer has them).  Both inputs are made before either half adds its output to the stream.  Layer norms
+    followed by convolutions of equal taps are one kernel for both halves, which reads the stream once."""
+    from ..ops import kernels
+    from .input_conv import CausalConvAdd
+    from .norm import LayerNorm
+    ctx.settle(x)
+    halves = [(layer.mixer, layer.mixer_norm, layer.mixer_input), (layer.feed_forward, layer.feed_forward_norm, layer.feed_forward_input)]
+    offsets = layer.state_offsets()
+    live = [(part, norm, filt, off) for (part, norm, filt), off in zip(halves, offsets) if part is not None]
+    state = ctx.state(cache_entry) if any(f is not None and f.state_elems() for _, _, f, _ in live) else None
+    fusable = (all(type(n) is LayerNorm and type(f) is CausalConvAdd for _, n, f, _ in live)
+               and len({(n.eps, f.spec.taps) for _, n, f, _ in live}) == 1
+               and live[0][2].spec.taps <= kernels.DUAL_NORM_CONV_MAX_TAPS)
+    if fusable:
+        if state is None:                                  # one tap: nothing is kept, the kernel is handed any float32 row
+            state = ctx.scratch.setdefault("no_state", x.new_zeros(1, 1))
+        inputs = kernels.dual_layernorm_conv(x, [(n.weight, n.bias, f.taps_weight, off) for _, n, f, off in live], live[0][1].eps,
+                                             state, ctx.tok_row, ctx.row_first, ctx.row_lens, ctx.slots, ctx.dtype, ctx.one_token_each)
+    else:
+        inputs = []
+        for _, norm, filt, off in live:
+            inputs.append(norm.forward(x, ctx.dtype) if filt is None
+                          else filt.apply(norm.forward(x, x.dtype), ctx, state, off, ctx.dtype))
+    for (part, _, _, _), h in zip(live, inputs):
+        if part is layer.mixer:
+            if hasattr(part, "add_output_to"):
+                part.add_output_to(x, h, ctx, entry, cache_entry, owns_cache)
+            else:
+                kernels.residual_add(x, part.apply(h, ctx, entry, cache_entry, owns_cache).contiguous())
+        elif hasattr(part, "add_output_to"):
+            part.add_output_to(x, h, ctx)
+        else:
+            kernels.residual_add(x, part.apply(h, ctx).contiguous())

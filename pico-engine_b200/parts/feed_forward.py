@@ -1,9 +1,9 @@
-"""Dense gated feed-forward."""
+"""Dense feed-forwards: gated (SwiGLU) and plain (up, activation, down)."""
 from __future__ import annotations
 
 import torch
 
-from ..config.specs import SwiGLUSpec
+from ..config.specs import ConfigError, DenseMLPSpec, SwiGLUSpec
 from ..ops import kernels, linear
 from ..weights.loader import ParamSpec
 from .base import FeedForward, register_feed_forward
@@ -50,3 +50,34 @@ class SwiGLU(FeedForward):
             return
         linear(self._activation(ctx.normed(x, norm), ctx), self.w_down, accumulate_into=x,
                defer_add=lambda y: ctx.defer_add(x, y))
+
+
+@register_feed_forward(DenseMLPSpec)
+class DenseMLP(FeedForward):
+    """down(act(up(h))) without biases; act is the square of relu, gelu (tanh formula) or silu, computed in float32."""
+
+    def __init__(self, spec: DenseMLPSpec, dtype, device):
+        super().__init__(spec, dtype, device)
+        if spec.activation not in kernels.ACTIVATIONS:
+            raise ConfigError(f"activation {spec.activation!r} is not known; known: {', '.join(sorted(kernels.ACTIVATIONS))}")
+        self.w_up = self.w_down = None
+
+    def expected_tensors(self):
+        s = self.spec
+        return {s.prefix + s.up_name: ParamSpec((s.intermediate, s.hidden)),
+                s.prefix + s.down_name: ParamSpec((s.hidden, s.intermediate))}
+
+    def take_tensors(self, get):
+        s = self.spec
+        self.w_up, self.w_down = get(s.prefix + s.up_name), get(s.prefix + s.down_name)
+
+    def _activation(self, h, ctx):
+        up = linear(h, self.w_up, out_dtype=ctx.dtype)
+        return kernels.activation(up, self.spec.activation, out=up)
+
+    def apply(self, h, ctx):
+        return linear(self._activation(h, ctx), self.w_down, out_dtype=ctx.dtype)
+
+    def add_output_to(self, x, h, ctx) -> None:
+        """x += feed_forward(h) for rows h that are normed (and filtered) already."""
+        linear(self._activation(h, ctx), self.w_down, accumulate_into=x)

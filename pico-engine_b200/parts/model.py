@@ -10,7 +10,7 @@ from ..cache import CacheNeeds
 from ..config.specs import ModelPlan
 from ..ops import kernels, linear
 from ..weights.loader import ParamSpec
-from .base import NORMS, StepContext, build_part
+from .base import NORMS, STREAM_POSITIONS, StepContext, build_part
 from .block import Layer
 
 
@@ -23,6 +23,8 @@ class DecoderModel:
         self.plan, self.dtype, self.device = plan, dtype, torch.device(device) if device != "meta" else device
         self.layers: List[Layer] = [Layer(s, dtype, self.device) for s in plan.layers]
         self.final_norm = build_part(NORMS, "norm", plan.final_norm, dtype, self.device)
+        self.embedding_position = None if plan.embedding_position is None else \
+            build_part(STREAM_POSITIONS, "stream position", plan.embedding_position, dtype, self.device)
         self.embedding: Optional[torch.Tensor] = None
         self.head: Optional[torch.Tensor] = None
 
@@ -31,6 +33,8 @@ class DecoderModel:
         for layer in self.layers:
             yield from layer.parts()
         yield self.final_norm
+        if self.embedding_position is not None:
+            yield self.embedding_position
 
     def expected_tensors(self) -> Dict[str, ParamSpec]:
         p = self.plan
@@ -54,13 +58,14 @@ class DecoderModel:
     # ------------------------------------------------------------------ cache
     def cache_needs(self) -> List[Optional[CacheNeeds]]:
         """Per schedule entry; None for an entry that reads another entry's cache."""
-        return [None if e.cache_of is not None or self.layers[e.layer].mixer is None
-                else self.layers[e.layer].mixer.cache_needs() for e in self.plan.schedule]
+        return [None if e.cache_of is not None else self.layers[e.layer].cache_needs() for e in self.plan.schedule]
 
     # ------------------------------------------------------------------ a step
     def hidden(self, token_ids: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         """The residual stream [T, hidden] float32 after the last layer."""
         x = kernels.embed(self.embedding, token_ids)
+        if self.embedding_position is not None:
+            self.embedding_position.add_to(x, ctx)
         for e, entry in enumerate(self.plan.schedule):
             cache_entry = e if entry.cache_of is None else entry.cache_of
             self.layers[entry.layer].run(x, ctx, e, cache_entry, entry.cache_of is None)
@@ -70,7 +75,10 @@ class DecoderModel:
     def logits(self, x: torch.Tensor, rows_index: torch.Tensor) -> torch.Tensor:
         """float32 logits [len(rows_index), vocab] of the rows ``rows_index`` of ``x``."""
         h = self.final_norm.forward(x, self.dtype, rows_index)
-        return linear(h, self.head, out_dtype=torch.float32)
+        logits = linear(h, self.head, out_dtype=torch.float32)
+        if self.plan.logit_softcap:
+            kernels.softcap(logits, self.plan.logit_softcap)
+        return logits
 
     def forward(self, token_ids: torch.Tensor, ctx: StepContext, rows_index: torch.Tensor) -> torch.Tensor:
         return self.logits(self.hidden(token_ids, ctx), rows_index)

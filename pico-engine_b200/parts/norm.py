@@ -1,7 +1,7 @@
-"""RMSNorm."""
+"""RMSNorm and layer norm."""
 from __future__ import annotations
 
-from ..config.specs import RMSNormSpec
+from ..config.specs import LayerNormSpec, RMSNormSpec
 from ..ops import kernels
 from ..weights.loader import ParamSpec
 from .base import Norm, register_norm
@@ -28,3 +28,27 @@ class RMSNorm(Norm):
 
     def add_forward(self, x, y, out_dtype):
         return kernels.add_rmsnorm(x, y, self.weight, self.eps, out_dtype)
+
+
+@register_norm(LayerNormSpec)
+class LayerNorm(Norm):
+    """y = (x - mean) / sqrt(var + eps) * w + b in float32, var the mean of the squared deviations."""
+
+    def __init__(self, spec: LayerNormSpec, dtype, device):
+        super().__init__(spec, dtype, device)
+        self.weight = self.bias = None
+        self.eps = spec.eps
+
+    def expected_tensors(self):
+        return {self.spec.weight: ParamSpec((self.spec.size,), init="one_plus_normal"),
+                self.spec.bias: ParamSpec((self.spec.size,))}
+
+    def take_tensors(self, get):
+        self.weight, self.bias = get(self.spec.weight), get(self.spec.bias)
+
+    def prepare(self, max_positions):
+        from ..ops.library import mixers
+        mixers()                                           # build or load this part's kernels now, loudly
+
+    def forward(self, x, out_dtype, rows_index=None):
+        return kernels.layernorm(x, self.weight, self.bias, self.eps, out_dtype, rows_index)

@@ -40,7 +40,8 @@ class UnusedWeightsWarning(UserWarning):
 @dataclass(frozen=True)
 class ParamSpec:
     """What a part expects of one tensor.  ``init`` names the distribution of the
-    random-weights mode: "normal" is N(0, 0.02), "one_plus_normal" is 1 + N(0, 0.02)."""
+    random-weights mode: "normal" is N(0, 0.02), "one_plus_normal" is 1 + N(0, 0.02), "identity_plus_normal" the
+    identity matrix + N(0, 0.02)."""
     shape: Tuple[int, ...]
     init: str = "normal"
 

@@ -31,6 +31,8 @@ def random_tensor(name: str, spec: ParamSpec, seed: int, store_dtype: torch.dtyp
     t = torch.randn(spec.shape, generator=g, device=device, dtype=torch.float32) * STD
     if spec.init == "one_plus_normal":
         t = t + 1.0
+    elif spec.init == "identity_plus_normal":           # a square matrix near the identity
+        t = t + torch.eye(spec.shape[0], spec.shape[1], device=device)
     elif spec.init != "normal":
         raise ValueError(f"tensor {name!r}: unknown init {spec.init!r}")
     return t.to(store_dtype)
