@@ -60,30 +60,41 @@ def input_conv(h, taps_weight):
 
 # ------------------------------------------------------------------ mixers
 
+def mixed_attention(q, k, v, scale, sink=None, talk=None, window=None):
+    """q [n, H, D], k [n, G, D], v [n, G, Dv] of one sequence -> [n, H, Dv].  Causal scores scale * q.k, a softmax
+    whose denominator also holds exp(sink_g), the heads' weights mixed by ``talk`` [H, H], each head's mixed weights
+    applied to the values of its own key/value head.  ``window`` w: query i sees keys i - w + 1 .. i."""
+    n, H, _ = q.shape
+    G, Dv = k.shape[1], v.shape[2]
+    per = H // G
+    weights = torch.zeros(H, n, n, dtype=q.dtype)          # weights[g, i, j], zero for unseen j
+    for g in range(H):
+        c = g // per
+        for i in range(n):
+            lo = 0 if window is None else max(0, i - window + 1)
+            s = (k[lo: i + 1, c] @ q[i, g]) * scale
+            top = float(s.max()) if sink is None else max(float(s.max()), float(sink[g]))
+            e = torch.exp(s - top)
+            den = e.sum() + (0.0 if sink is None else math.exp(float(sink[g]) - top))
+            weights[g, i, lo: i + 1] = e / den
+    mixed = weights if talk is None else torch.einsum("hg,gij->hij", talk, weights)
+    out = torch.zeros(n, H, Dv, dtype=q.dtype)
+    for hd in range(H):
+        out[:, hd] = mixed[hd] @ v[:, hd // per]
+    return out
+
+
 def attention_mixer(h, w, prefix, m, eps):
-    """Grouped softmax attention without positions, with query/key norm, a sink in the denominator and
-    mixing of the heads' weights.  ``m`` is the layer's mixer dictionary of config.json."""
+    """Projections with biases, RMS norm of every query and key head (one weight vector for all heads), the
+    attention above, the output projection.  ``m`` is the layer's mixer dictionary of config.json."""
     n = h.shape[0]
-    H, G, D, Dv, scale = m["heads"], m["kv_heads"], m["dim"], m["vdim"], m["scale"]
+    H, G, D, Dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     q = (h @ w[prefix + "q"].T + w[prefix + "q.b"]).view(n, H, D)
     k = (h @ w[prefix + "k"].T + w[prefix + "k.b"]).view(n, G, D)
     v = (h @ w[prefix + "v"].T + w[prefix + "v.b"]).view(n, G, Dv)
     q = rms_norm(q, w[prefix + "q.norm"], eps)
     k = rms_norm(k, w[prefix + "k.norm"], eps)
-    sink, talk = w[prefix + "sink"], w[prefix + "talk"]
-    per = H // G
-    weights = torch.zeros(H, n, n, dtype=h.dtype)          # weights[g, i, j], zero for j > i
-    for g in range(H):
-        c = g // per
-        for i in range(n):
-            s = (k[: i + 1, c] @ q[i, g]) * scale
-            top = max(float(s.max()), float(sink[g]))
-            e = torch.exp(s - top)
-            weights[g, i, : i + 1] = e / (e.sum() + math.exp(float(sink[g]) - top))
-    mixed = torch.einsum("hg,gij->hij", talk, weights)
-    out = torch.zeros(n, H, Dv, dtype=h.dtype)
-    for hd in range(H):
-        out[:, hd] = mixed[hd] @ v[:, hd // per]
+    out = mixed_attention(q, k, v, m["scale"], w[prefix + "sink"], w[prefix + "talk"])
     return out.reshape(n, H * Dv) @ w[prefix + "o"].T
 
 
@@ -92,19 +103,24 @@ def mingru_candidate(u):
     return torch.where(u >= 0, u + 0.5, torch.sigmoid(u))
 
 
+def mingru_recurrence(pz, pu, pg, S0=None):
+    """Rows of pre-activations [n, W] -> (S_t * silu(pg_t) for every t, the last S)."""
+    z = torch.sigmoid(pz)
+    c = mingru_candidate(pu)
+    gate = pg * torch.sigmoid(pg)
+    S = torch.zeros(pz.shape[1], dtype=pz.dtype) if S0 is None else S0
+    rows = []
+    for t in range(pz.shape[0]):
+        S = (1 - z[t]) * S + z[t] * c[t]
+        rows.append(S * gate[t])
+    return torch.stack(rows), S
+
+
 def mingru_mixer(h, w, prefix):
     """S_t = (1 - z_t) S_(t-1) + z_t c_t from S = 0; output W_o (S_t * silu(W_g h_t))."""
-    n = h.shape[0]
-    z = torch.sigmoid(h @ w[prefix + "z"].T + w[prefix + "z.b"])
-    c = mingru_candidate(h @ w[prefix + "x"].T + w[prefix + "x.b"])
-    g = h @ w[prefix + "g"].T
-    g = g * torch.sigmoid(g)
-    S = torch.zeros(z.shape[1], dtype=h.dtype)
-    rows = []
-    for t in range(n):
-        S = (1 - z[t]) * S + z[t] * c[t]
-        rows.append(S * g[t])
-    return torch.stack(rows) @ w[prefix + "o"].T
+    y, _ = mingru_recurrence(h @ w[prefix + "z"].T + w[prefix + "z.b"], h @ w[prefix + "x"].T + w[prefix + "x.b"],
+                             h @ w[prefix + "g"].T)
+    return y @ w[prefix + "o"].T
 
 
 # ------------------------------------------------------------------ feed-forward
