@@ -1,0 +1,209 @@
+"""Two designs side by side at equal layer widths: the Mebalorn decoder (layer norm + input convolution, attention
+with mixed heads or a minGRU recurrence, a dense relu^2 feed-forward, both halves in parallel) and the dense Qwen2
+decoder, this library's closest other model.  Random weights; prefill and decode throughput of a few layers, and
+the kernels of the new design each beside the Qwen2 kernel that does the like job, as fractions of the measured
+copy bandwidth or matrix throughput.
+
+    python -m pico_engine.design_compare [--sizes s,m,l] [--tokens 2048] [--batch 8] [--context 2048] [--output FILE]
+"""
+from __future__ import annotations
+
+import argparse
+import json
+from typing import Callable, Dict
+
+import torch
+
+from . import benchmark as B
+from .config import config_from_dict
+from .ops import kernels
+
+# layer widths that resemble real models: (width, heads, key/value heads, head size, feed-forward width, layers)
+SIZES = {"s": (896, 14, 2, 64, 4864, 4), "m": (2048, 16, 4, 128, 8192, 4), "l": (3584, 28, 4, 128, 18944, 2)}
+VOCAB = 32768
+TAPS = 4
+
+
+def mebalorn_config(size: str) -> dict:
+    W, H, G, D, F, L = SIZES[size]
+    att = {"type": "attention", "mixer": {"heads": H, "kv_heads": G, "dim": D, "vdim": D, "scale": D ** -0.5}, "mlp": {"kind": "dense", "ff": F}}
+    rec = {"type": "mingru", "mixer": {"width": W}, "mlp": {"kind": "dense", "ff": F}}
+    return {"architecture": "Mebalorn", "vocab": VOCAB, "width": W, "canon": {"taps": TAPS}, "norm": {"eps": 1e-6},
+            "logit_softcap": 30.0, "layers": [rec if i % 2 == 0 else att for i in range(L)]}
+
+
+def qwen2_config(size: str) -> dict:
+    W, H, G, D, F, L = SIZES[size]
+    return {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "hidden_act": "silu", "torch_dtype": "bfloat16",
+            "num_hidden_layers": L, "hidden_size": W, "num_attention_heads": H, "num_key_value_heads": G, "head_dim": D,
+            "intermediate_size": F, "vocab_size": VOCAB, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6,
+            "max_position_embeddings": 32768, "tie_word_embeddings": False, "use_sliding_window": False}
+
+
+_flush = {}
+
+
+def device_us(fn: Callable[[], object], repetitions: int = 7) -> float:
+    """Median microseconds of ``fn`` on the device, CUDA events around it, the L2 flushed before every call
+    (a 256 MB buffer is written), two warm-up calls."""
+    buf = _flush.get("buf")
+    if buf is None:
+        buf = _flush["buf"] = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    times = []
+    for i in range(repetitions + 2):
+        buf.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        e1.synchronize()
+        if i >= 2:
+            times.append(e0.elapsed_time(e1) * 1000.0)
+    return B.percentile(times, 50)
+
+
+def _prompt_context(eng, tokens: int):
+    slot = eng.cache.open()
+    ids = torch.randint(0, eng.model.plan.vocab_size, (tokens,), generator=torch.Generator().manual_seed(0)).tolist()
+    eng.stepper.step([slot], [ids], [[]])                     # fills the cache and the states of this slot
+    eng.cache.close(slot)
+    slot = eng.cache.open()
+    lay, host, starts = eng.stepper.describe([slot], [tokens], None, [ids])
+    dev = eng.stepper.upload(host)
+    return slot, eng.stepper.context(lay, dev, [tokens], starts, [slot])
+
+
+def _decode_context(eng, batch: int, context: int):
+    slots = B.open_sequences(eng, batch, context - 1)
+    lay, host, starts = eng.stepper.describe(slots, [1] * batch, None, [[1]] * batch)
+    dev = eng.stepper.upload(host)
+    return slots, eng.stepper.context(lay, dev, [1] * batch, starts, slots)
+
+
+def kernel_times(size: str, tokens: int, batch: int, context: int, peaks: dict) -> Dict[str, dict]:
+    """Every kernel of the new design beside the like kernel of the Qwen2 decoder: microseconds, the bytes or
+    multiply-adds it must move or do, and that as a fraction of the measured peak."""
+    from .engine.engine import Engine
+    W, H, G, D, F, L = SIZES[size]
+    out: Dict[str, dict] = {}
+    bf = torch.bfloat16
+
+    def entry(name, us, nbytes=None, flops=None):
+        rec = {"us": us}
+        if nbytes is not None:
+            rec.update(gbytes_per_s=nbytes / us / 1e3, frac=nbytes / us / 1e3 / peaks["hbm_gbs"], bound="hbm")
+        if flops is not None:
+            rec.update(tflops_per_s=flops / us / 1e6, frac=flops / us / 1e6 / peaks["bf16_tflops"], bound="bf16")
+        out[name] = rec
+
+    for design, cfg in (("mebalorn", mebalorn_config(size)), ("qwen2", qwen2_config(size))):
+        eng = Engine.from_config(config_from_dict(cfg), seed=1, draw_on="cuda", dtype="bfloat16")
+        eng.ensure_cache(max(tokens, batch * context) + 64 * batch, max(tokens, context), max_seqs=batch + 1)
+        e_att = next(e for e, s in enumerate(eng.model.plan.schedule) if hasattr(eng.model.layers[s.layer].mixer.spec, "n_heads"))
+        att = eng.model.layers[e_att].mixer
+        seen = tokens * (tokens + 1) / 2
+        # ---- a prompt of `tokens`
+        slot, ctx = _prompt_context(eng, tokens)
+        kv = ctx.kv(e_att)
+        x = torch.randn(tokens, W, device="cuda")
+        qkv = torch.randn(tokens, (H + 2 * G) * D, device="cuda").to(bf)
+        if design == "mebalorn":
+            layer = eng.model.layers[e_att]
+            state = ctx.state(e_att)
+            halves = [(n.weight, n.bias, f.taps_weight, o) for n, f, o in zip((layer.mixer_norm, layer.feed_forward_norm),
+                      (layer.mixer_input, layer.feed_forward_input), layer.state_offsets())]
+            entry("prefill norm+conv, both halves", device_us(lambda: kernels.dual_layernorm_conv(
+                x, halves, 1e-6, state, ctx.tok_row, ctx.row_first, ctx.row_lens, ctx.slots, bf, False)), nbytes=tokens * W * (4 + 2 * 2))
+            entry("prefill attention (mixed heads)", device_us(lambda: kernels.attention_headmix(
+                qkv, qkv.shape[1], H, G, D, D, kv.k, kv.v, kv.table, kv.stride, ctx.tok_pos, ctx.tok_row, None, D ** -0.5, att.sink,
+                att.head_mix, ctx)), flops=4.0 * H * D * seen)
+            e_rec = next(e for e, s in enumerate(eng.model.plan.schedule) if not hasattr(eng.model.layers[s.layer].mixer.spec, "n_heads"))
+            proj = torch.randn(tokens, 3 * W, device="cuda").to(bf)
+            entry("prefill recurrence", device_us(lambda: kernels.mingru(proj, ctx.state(e_rec), 0, ctx.tok_row, ctx.row_first, ctx.row_lens,
+                                                                        ctx.slots, chunked=True)), nbytes=tokens * W * 2 * 4)
+            up = torch.randn(tokens, F, device="cuda").to(bf)
+            entry("prefill relu^2", device_us(lambda: kernels.activation(up, "relu2", out=up)), nbytes=tokens * F * 2 * 2)
+            entry("prefill q/k norm + cache write", device_us(lambda: kernels.qknorm_store(
+                qkv, H, G, D, D, att.q_norm, att.k_norm, 1e-6, ctx.tok_pos, ctx.tok_row, kv.k, kv.v, kv.table, kv.stride)),
+                nbytes=tokens * (H + 2 * G) * D * 2 * 2)
+        else:
+            norm = eng.model.layers[0].mixer_norm
+            entry("qwen2 prefill rmsnorm, twice", device_us(lambda: (kernels.rmsnorm(x, norm.weight, 1e-6, bf), kernels.rmsnorm(x, norm.weight, 1e-6, bf))),
+                  nbytes=tokens * W * 2 * (4 + 2))
+            entry("qwen2 prefill attention", device_us(lambda: kernels.attention(
+                qkv, qkv.shape[1], H, G, D, kv.k, kv.v, kv.table, kv.stride, ctx.tok_pos, ctx.tok_row, None, D ** -0.5, ctx)),
+                flops=4.0 * H * D * seen)
+            gu = torch.randn(tokens, 2 * F, device="cuda").to(bf)
+            entry("qwen2 prefill swiglu", device_us(lambda: kernels.swiglu(gu)), nbytes=tokens * F * 2 * 3)
+            cos, sin = att._tables(ctx)
+            entry("qwen2 prefill rope + cache write", device_us(lambda: kernels.rope_store(
+                qkv, H, G, D, cos, sin, ctx.tok_pos, ctx.tok_row, kv.k, kv.v, kv.table, kv.stride)), nbytes=tokens * (H + 2 * G) * D * 2 * 2)
+        eng.cache.close(slot)
+        # ---- a step of `batch` single tokens at `context`
+        slots, ctx = _decode_context(eng, batch, context)
+        kv = ctx.kv(e_att)
+        q1 = torch.randn(batch, (H + 2 * G) * D, device="cuda").to(bf)
+        kv_bytes = batch * context * 2 * G * D * 2
+        if design == "mebalorn":
+            entry("decode attention (mixed heads)", device_us(lambda: kernels.attention_headmix(
+                q1, q1.shape[1], H, G, D, D, kv.k, kv.v, kv.table, kv.stride, ctx.tok_pos, ctx.tok_row, None, D ** -0.5, att.sink,
+                att.head_mix, ctx)), nbytes=kv_bytes)
+        else:
+            entry("qwen2 decode attention", device_us(lambda: kernels.attention(
+                q1, q1.shape[1], H, G, D, kv.k, kv.v, kv.table, kv.stride, ctx.tok_pos, ctx.tok_row, None, D ** -0.5, ctx)), nbytes=kv_bytes)
+        B.close_sequences(eng, slots)
+        kernels.check_status(eng.device)
+        del eng, ctx, kv
+        torch.cuda.empty_cache()
+    return out
+
+
+def throughput(size: str, tokens: int, batch: int, context: int, steps: int = 64) -> Dict[str, dict]:
+    """Prefill of one prompt and decode of ``batch`` sequences through the engines' own steps, both designs."""
+    from .engine.engine import Engine
+    out = {}
+    for design, cfg in (("mebalorn", mebalorn_config(size)), ("qwen2", qwen2_config(size))):
+        eng = Engine.from_config(config_from_dict(cfg), seed=1, draw_on="cuda", dtype="bfloat16")
+        pre = B.prefill_device(eng, tokens)
+        dec = B.decode_device(eng, batch, context, steps, 4)
+        out[design] = {"prefill_tokens_per_s": pre["tokens_per_s"], "prefill_ms": pre["ms"], "prefill_tflops_per_s": pre["tflops_per_s"],
+                       "decode_tokens_per_s": dec["tokens_per_s"], "decode_ms_per_step": dec["ms_per_step"],
+                       "decode_gbytes_per_s": dec["gbytes_per_s"], "decode_launches_per_step": dec["launches_per_step"],
+                       "weight_bytes": eng.model.step_weight_bytes()}
+        del eng
+        torch.cuda.empty_cache()
+    return out
+
+
+def compare(sizes, tokens: int, batch: int, context: int, peaks: dict) -> dict:
+    record = {"tokens": tokens, "batch": batch, "context": context, "layers": {s: SIZES[s][5] for s in sizes},
+              "widths": {s: dict(zip(("width", "heads", "kv_heads", "head_dim", "ff"), SIZES[s][:5])) for s in sizes}, "sizes": {}}
+    for s in sizes:
+        record["sizes"][s] = {"throughput": throughput(s, tokens, batch, context), "kernels": kernel_times(s, tokens, batch, context, peaks)}
+    return record
+
+
+def main(argv=None) -> None:
+    p = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    p.add_argument("--sizes", default="s,m")
+    p.add_argument("--tokens", type=int, default=2048)
+    p.add_argument("--batch", type=int, default=8)
+    p.add_argument("--context", type=int, default=2048)
+    p.add_argument("--hbm-gbs", type=float, default=6650.0)
+    p.add_argument("--bf16-tflops", type=float, default=1590.0)
+    p.add_argument("--output")
+    a = p.parse_args(argv)
+    rec = compare([s for s in a.sizes.split(",") if s], a.tokens, a.batch, a.context, {"hbm_gbs": a.hbm_gbs, "bf16_tflops": a.bf16_tflops})
+    for s, r in rec["sizes"].items():
+        for d, t in r["throughput"].items():
+            print(f"{s} {d}: prefill {t['prefill_tokens_per_s']:.0f} tok/s ({t['prefill_ms']:.2f} ms), decode {t['decode_tokens_per_s']:.0f} tok/s "
+                  f"({t['decode_ms_per_step']:.3f} ms a step, {t['decode_launches_per_step']} launches)")
+        for k, t in r["kernels"].items():
+            print(f"{s} {k}: {t['us']:.1f} us, {t['frac']:.3f} of the {t['bound']} peak")
+    if a.output:
+        with open(a.output, "w") as f:
+            json.dump(rec, f, indent=1)
+
+
+if __name__ == "__main__":
+    main()

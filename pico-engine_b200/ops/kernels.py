@@ -802,6 +802,21 @@ def qknorm_store(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, v_he
                                    1 if store else 0, stream_ptr()), "qknorm_store")
 
 
+HEADMIX_TENSOR_CORES = os.environ.get("PICO_ENGINE_HEADMIX_MMA", "1") != "0"      # 0: bfloat16 too runs the float32-FMA kernel
+_headmix_plans = {}
+
+
+def headmix_mma_key_block(n_heads: int, n_kv: int, head_dim: int, v_head_dim: int) -> int:
+    """Keys a block of the tensor-core kernel visits at a time for these sizes; 0: it does not take them (more than 32
+    heads, or a tile that does not fit the shared memory), and the float32-FMA kernel runs."""
+    key = (n_heads, n_kv, head_dim, v_head_dim)
+    if key not in _headmix_plans:
+        import ctypes
+        dvs = ctypes.c_int(1)
+        _headmix_plans[key] = mixers().pe_attention_headmix_mma_plan(n_heads, n_kv, head_dim, v_head_dim, ctypes.byref(dvs))
+    return _headmix_plans[key]
+
+
 def attention_headmix(q: torch.Tensor, q_stride: int, n_heads: int, n_kv: int, head_dim: int, v_head_dim: int,
                       k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor, table_stride: int,
                       tok_pos: torch.Tensor, tok_row: torch.Tensor, window: Optional[int], scale: float,
@@ -823,6 +838,21 @@ def attention_headmix(q: torch.Tensor, q_stride: int, n_heads: int, n_kv: int, h
         if tiles is None:
             tiles = ctx.scratch["prefill_tiles"] = prefill_tiles(ctx.lens, ctx.starts, q.device, PREFILL_TILE)
         n_runs = tiles.shape[0]
+    from .workspace import scratch
+    out = torch.empty(T, n_heads * v_head_dim, dtype=q.dtype, device=q.device)
+    if q.dtype == torch.bfloat16 and HEADMIX_TENSOR_CORES:
+        kb = headmix_mma_key_block(n_heads, n_kv, head_dim, v_head_dim)
+        if kb and all(t is None or t.dtype == torch.float32 for t in (sink, mix)):
+            # bfloat16: the tensor-core kernel; tiles of 16 tokens, ranges of at least two key blocks
+            n_tiles = T if tiles is None else n_runs * (PREFILL_TILE // 16)
+            splits = 1 if n_tiles >= 148 else max(1, min(296 // n_tiles, (ctx.max_context + 2 * kb - 1) // (2 * kb), 64))
+            ws = scratch("attention_headmix", 4 * lib.pe_attention_headmix_mma_scratch_floats(n_tiles, splits, n_heads, v_head_dim), q.device)
+            check(lib.pe_attention_headmix_mma(q.data_ptr(), q_stride, out.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(),
+                                               block_table.data_ptr(), table_stride, tok_pos.data_ptr(), tok_row.data_ptr(),
+                                               _ptr(tiles), n_runs, PREFILL_TILE, T, n_heads, n_kv, head_dim, v_head_dim,
+                                               window or 0, float(scale), _ptr(sink), _ptr(mix), splits, ws.data_ptr(), stream_ptr()),
+                  "attention_headmix_mma", 1 if splits == 1 else 3)
+            return out
     qt = lib.pe_attention_headmix_tile(n_heads, n_kv, head_dim, v_head_dim, 0 if mix is None else 1, 1 if tiles is None else 16)
     if qt <= 0:
         raise KernelError(f"attention with {n_heads} heads of size {head_dim}/{v_head_dim} is not taken: heads x value size "
@@ -832,9 +862,7 @@ def attention_headmix(q: torch.Tensor, q_stride: int, n_heads: int, n_kv: int, h
     splits = 1
     if n_tiles < 296:
         splits = max(1, min(296 // max(n_tiles, 1), (ctx.max_context + 255) // 256, 64))
-    from .workspace import scratch
     ws = scratch("attention_headmix", 4 * lib.pe_attention_headmix_scratch_floats(n_tiles, splits, qt, n_heads, v_head_dim), q.device)
-    out = torch.empty(T, n_heads * v_head_dim, dtype=q.dtype, device=q.device)
     check(lib.pe_attention_headmix(q.data_ptr(), q_stride, out.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), _code(q, "q"),
                                    block_table.data_ptr(), table_stride, tok_pos.data_ptr(), tok_row.data_ptr(), _ptr(tiles),
                                    n_runs, PREFILL_TILE, T, n_heads, n_kv, head_dim, v_head_dim, window or 0, float(scale),
