@@ -43,23 +43,47 @@ def qwen2_config(size: str) -> dict:
 _flush = {}
 
 
-def device_us(fn: Callable[[], object], repetitions: int = 7) -> float:
-    """Median microseconds of ``fn`` on the device, CUDA events around it, the L2 flushed before every call
-    (a 256 MB buffer is written), two warm-up calls."""
+def _graph_ms(body: Callable[[], object], replays: int = 5) -> float:
+    """Median milliseconds of a replay of the CUDA graph that ``body`` records."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            body()
+    torch.cuda.current_stream().wait_stream(side)
+    graph.replay()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(replays):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        graph.replay()
+        e1.record()
+        e1.synchronize()
+        times.append(e0.elapsed_time(e1))
+    return B.percentile(times, 50)
+
+
+def device_us(fn: Callable[[], object], calls: int = 8) -> float:
+    """Microseconds of ``fn`` on the device.  ``calls`` times [write a 256 MB buffer (which empties the L2), fn] are
+    captured in one CUDA graph, so that no launch waits for the host; the same graph without fn is timed too and
+    subtracted.  CUDA events around the replays, the median of five, after a warm-up call and replay."""
     buf = _flush.get("buf")
     if buf is None:
         buf = _flush["buf"] = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
-    times = []
-    for i in range(repetitions + 2):
-        buf.zero_()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        fn()
-        e1.record()
-        e1.synchronize()
-        if i >= 2:
-            times.append(e0.elapsed_time(e1) * 1000.0)
-    return B.percentile(times, 50)
+    fn()
+    torch.cuda.synchronize()
+
+    def both():
+        for _ in range(calls):
+            buf.zero_()
+            fn()
+
+    def flush_only():
+        for _ in range(calls):
+            buf.zero_()
+    return max(0.0, (_graph_ms(both) - _graph_ms(flush_only)) * 1000.0 / calls)
 
 
 def _prompt_context(eng, tokens: int):

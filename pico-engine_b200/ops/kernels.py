@@ -802,7 +802,10 @@ def qknorm_store(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, v_he
                                    1 if store else 0, stream_ptr()), "qknorm_store")
 
 
-HEADMIX_TENSOR_CORES = os.environ.get("PICO_ENGINE_HEADMIX_MMA", "1") != "0"      # 0: bfloat16 too runs the float32-FMA kernel
+# Which kernel runs head-mixing attention in bfloat16: "1" the one-pass tensor-core kernel (attention_headmix_flash.cu) where
+# it takes the sizes, else the two-pass one (attention_headmix_mma.cu), else float32 FMAs; "two-pass" and "0" skip the first
+# or both (the tests run all three).
+HEADMIX_TENSOR_CORES = os.environ.get("PICO_ENGINE_HEADMIX_MMA", "1")
 _headmix_plans = {}
 
 
@@ -840,9 +843,25 @@ def attention_headmix(q: torch.Tensor, q_stride: int, n_heads: int, n_kv: int, h
         n_runs = tiles.shape[0]
     from .workspace import scratch
     out = torch.empty(T, n_heads * v_head_dim, dtype=q.dtype, device=q.device)
-    if q.dtype == torch.bfloat16 and HEADMIX_TENSOR_CORES:
+    floats = all(t is None or t.dtype == torch.float32 for t in (sink, mix))
+    if q.dtype == torch.bfloat16 and HEADMIX_TENSOR_CORES == "1" and floats:
+        cg = lib.pe_attention_flashmix_group(n_heads, n_kv, head_dim, v_head_dim)
+        if cg and q_stride % 2 == 0:
+            # one pass over the keys with an output for every (head, value head), then merge + sink + mixing
+            blocks = (n_runs * n_heads if tiles is not None else T * n_kv) * ((n_kv + cg - 1) // cg)
+            # enough blocks to fill the GPU; long prompts are cut too, so that the last rows' blocks (which see the most
+            # keys) do not run on after all others have ended
+            splits = max(1, min((ctx.max_context + 1023) // 1024, 8)) if blocks >= 296 else \
+                max(1, min((296 + blocks - 1) // blocks, (ctx.max_context + 127) // 128, 64))
+            ws = scratch("attention_headmix", 4 * lib.pe_attention_flashmix_scratch_floats(T, splits, n_heads, n_kv, v_head_dim), q.device)
+            check(lib.pe_attention_flashmix(q.data_ptr(), q_stride, out.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(),
+                                            block_table.data_ptr(), table_stride, tok_pos.data_ptr(), tok_row.data_ptr(), _ptr(tiles),
+                                            n_runs, T, n_heads, n_kv, head_dim, v_head_dim, window or 0, float(scale), _ptr(sink),
+                                            _ptr(mix), splits, ws.data_ptr(), stream_ptr()), "attention_flashmix", 2)
+            return out
+    if q.dtype == torch.bfloat16 and HEADMIX_TENSOR_CORES in ("1", "two-pass") and floats:
         kb = headmix_mma_key_block(n_heads, n_kv, head_dim, v_head_dim)
-        if kb and all(t is None or t.dtype == torch.float32 for t in (sink, mix)):
+        if kb:
             # bfloat16: the tensor-core kernel; tiles of 16 tokens, ranges of at least two key blocks
             n_tiles = T if tiles is None else n_runs * (PREFILL_TILE // 16)
             splits = 1 if n_tiles >= 148 else max(1, min(296 // n_tiles, (ctx.max_context + 2 * kb - 1) // (2 * kb), 64))

@@ -19,7 +19,8 @@ CORE_SOURCES = ("elementwise.cu", "linear_simt.cu", "attention_generic.cu", "sam
 EXTRA_SOURCES = ("linear_mma.cu", "linear_batch.cu", "gemm_splitk.cu")
 # The kernels of parts that only some designs have (layer norm with the short convolution on a sublayer's input, attention
 # whose weights are mixed across heads, the gated recurrence): compiled when a model with such a part is built.
-MIXER_SOURCES = ("layernorm_conv.cu", "attention_headmix.cu", "attention_headmix_mma.cu", "gated_recurrence.cu")
+MIXER_SOURCES = ("layernorm_conv.cu", "attention_headmix.cu", "attention_headmix_mma.cu", "attention_headmix_flash.cu",
+                 "gated_recurrence.cu")
 HEAD_DIM_SOURCES = ("attention_decode.cu", "attention_prefill.cu", "attention_prefill_tcgen05.cu")      # compiled per head size
 
 _SIGNATURES = {
@@ -53,6 +54,7 @@ _MIXER_SIGNATURES = {
     "pe_mingru": [P, I, P, LL, P, P, P, P, P, I, I, I, I, P, P],
     "pe_attention_headmix": [P, I, P, P, P, I, P, I, P, P, P, I, I, I, I, I, I, I, I, F, P, I, P, I, I, I, P, P],
     "pe_qknorm_store": [P, I, I, I, I, I, I, P, I, P, I, F, P, P, P, P, P, I, I, P],
+    "pe_attention_flashmix": [P, I, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, P, P, I, P, P],
     "pe_attention_headmix_mma": [P, I, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, F, P, P, I, P, P],
 }
 
@@ -125,6 +127,10 @@ def mixers() -> ctypes.CDLL:
         lib.pe_attention_headmix_tile.restype = c_int
         lib.pe_attention_headmix_scratch_floats.argtypes = [I, I, I, I, I]
         lib.pe_attention_headmix_scratch_floats.restype = c_longlong
+        lib.pe_attention_flashmix_group.argtypes = [I, I, I, I]
+        lib.pe_attention_flashmix_group.restype = c_int
+        lib.pe_attention_flashmix_scratch_floats.argtypes = [I, I, I, I, I]
+        lib.pe_attention_flashmix_scratch_floats.restype = c_longlong
         lib.pe_attention_headmix_mma_plan.argtypes = [I, I, I, I, ctypes.POINTER(c_int)]
         lib.pe_attention_headmix_mma_plan.restype = c_int
         lib.pe_attention_headmix_mma_scratch_floats.argtypes = [I, I, I, I]
