@@ -66,8 +66,8 @@ def main(argv=None) -> None:
         if args.layers is not None:
             if args.layers < 1:
                 p.error("--layers must be at least 1")
-            d["num_hidden_layers"] = args.layers
-            d["max_window_layers"] = min(d.get("max_window_layers", args.layers), args.layers)
+            from .config.shapes import with_layers
+            d = with_layers(d, args.layers)
         config = config_from_dict(d)
     elif args.layers is not None:
         p.error("--layers goes with --random-config")

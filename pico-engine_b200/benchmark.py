@@ -419,7 +419,8 @@ def main(argv=None) -> None:
         from .config.shapes import shape
         d = shape(args.random)
         if args.layers:
-            d["num_hidden_layers"] = args.layers
+            from .config.shapes import with_layers
+            d = with_layers(d, args.layers)
         eng = Engine.from_config(config_from_dict(d), seed=args.seed, draw_on="cuda", dtype=args.dtype)
     else:
         eng = Engine(args.model, dtype=args.dtype)

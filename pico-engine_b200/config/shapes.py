@@ -1,5 +1,5 @@
 """config.json contents of the shapes the benchmarks and tests name: the two tiny test
-configurations and the Qwen2.5 sizes (weights for them are drawn at random)."""
+configurations, the Qwen2.5 sizes and Mebalorn models at the same widths (weights for them are drawn at random)."""
 from __future__ import annotations
 
 _QWEN2 = {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "hidden_act": "silu", "torch_dtype": "bfloat16"}
@@ -25,6 +25,38 @@ SHAPES = {
                     "rope_theta": 1000000.0, "rms_norm_eps": 1e-5, "max_position_embeddings": 32768,
                     "tie_word_embeddings": False, "use_sliding_window": False},
 }
+
+
+def mebalorn_shape(width: int, heads: int, kv_heads: int, dim: int, ff: int, layers: int, vocab: int, taps: int = 4,
+                   vdim: int | None = None, softcap: float | None = 30.0) -> dict:
+    """A Mebalorn config.json: recurrent and attention layers in turn (the first is recurrent), every layer with a
+    feed-forward, the recurrent state as wide as the model."""
+    att = {"type": "attention", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim or dim, "scale": dim ** -0.5},
+           "mlp": {"kind": "dense", "ff": ff}}
+    rec = {"type": "mingru", "mixer": {"width": width}, "mlp": {"kind": "dense", "ff": ff}}
+    d = {"architecture": "Mebalorn", "vocab": vocab, "width": width, "canon": {"taps": taps}, "norm": {"eps": 1e-6},
+         "layers": [dict(rec if i % 2 == 0 else att) for i in range(layers)]}
+    if softcap:
+        d["logit_softcap"] = softcap
+    return d
+
+
+SHAPES.update({
+    "mebalorn-tiny": mebalorn_shape(64, 4, 2, 16, 160, 4, 256, taps=3, vdim=32),
+    "mebalorn-0.5b": mebalorn_shape(896, 14, 2, 64, 4864, 24, 151936),          # the widths of qwen2.5-0.5b
+    "mebalorn-7b": mebalorn_shape(3584, 28, 4, 128, 18944, 28, 152064),         # the widths of qwen2.5-7b
+})
+
+
+def with_layers(d: dict, n: int) -> dict:
+    """The shape with only its first ``n`` layers."""
+    d = dict(d)
+    if isinstance(d.get("layers"), list):
+        d["layers"] = d["layers"][:n]
+    else:
+        d["num_hidden_layers"] = n
+        d["max_window_layers"] = min(d.get("max_window_layers", n), n)
+    return d
 
 
 def shape(name: str) -> dict:

@@ -269,34 +269,71 @@ __global__ void __launch_bounds__(FX_THREADS, (NVM <= 16 && DKM <= 8) ? 3 : 2) f
 }
 
 // out[t][h] = sum_g mix[h, g] * (sum over ranges of O'_g,c(h) * exp(m - M_g)) / (sum over ranges of l * exp(m - M_g) + exp(sink_g - M_g)).
-// A block per (token, head), a thread per value column; the H x ranges loads of a thread do not depend on one another.
-__global__ void __launch_bounds__(256) flashmix_merge_kernel(FlashMixArgs a, const float* sink, const float* mix, bf16* out) {
+// A block has R groups of Dv threads (a thread a value column).  With many (range, head) pairs to add (single tokens with
+// long contexts: `share` = 1) a block takes one (token, head) and deals the pairs to its groups, whose sums meet in shared
+// memory in the order of the groups; with few (prompts) every group takes a head of its own.  A thread's loads do not
+// depend on one another; eight are in flight at a time.
+__global__ void __launch_bounds__(256) flashmix_merge_kernel(FlashMixArgs a, const float* sink, const float* mix, bf16* out, int share) {
     pdl_launch_dependents();
     pdl_wait();
-    extern __shared__ float coef[];                           // [H][splits]: mix[h, g] * exp(m_s - M_g) / denominator_g
-    const int t = blockIdx.x, h = blockIdx.y, H = a.H, G = a.G, Dv = a.Dv, per_kv = H / G, S = a.splits;
-    const int c = h / per_kv;
-    for (int g = threadIdx.x; g < H; g += blockDim.x) {
-        const float w = mix ? mix[h * H + g] : (g == h ? 1.f : 0.f);
-        const float* pm = a.pm + (size_t)t * S * H + g;
-        const float* pl = a.pl + (size_t)t * S * H + g;
-        float M = sink ? sink[g] : -INFINITY;
-        for (int s = 0; s < S; ++s) M = fmaxf(M, pm[(size_t)s * H]);
-        float den = sink ? expf(sink[g] - M) : 0.f;
-        for (int s = 0; s < S; ++s) if (pm[(size_t)s * H] > -INFINITY) den += pl[(size_t)s * H] * expf(pm[(size_t)s * H] - M);
-        const float inv = den > 0.f ? w / den : 0.f;
-        for (int s = 0; s < S; ++s) coef[g * S + s] = pm[(size_t)s * H] > -INFINITY ? expf(pm[(size_t)s * H] - M) * inv : 0.f;
+    extern __shared__ float merge_s[];
+    const int t = blockIdx.x, H = a.H, G = a.G, Dv = a.Dv, per_kv = H / G, S = a.splits;
+    float* coef = merge_s;                                    // [splits][H]: first the ranges' maxima, then exp(m - M_g) / denominator_g
+    float* pl_s = coef + S * H;                               // [splits][H]: the ranges' sums
+    float* M_s = pl_s + S * H;                                // [H]
+    float* inv_s = M_s + H;                                   // [H]
+    float* red = inv_s + H;                                   // [R][Dv]
+    for (int e = threadIdx.x; e < S * H; e += blockDim.x) {   // all loads at once, not one after the other
+        coef[e] = a.pm[(size_t)t * S * H + e];
+        pl_s[e] = a.pl[(size_t)t * S * H + e];
     }
     __syncthreads();
-    const float* po = a.po + (size_t)t * S * H * G * Dv + (size_t)c * Dv;
-    const int g_lo = mix ? 0 : h, g_hi = mix ? H : h + 1;
-    for (int d = threadIdx.x; d < Dv; d += blockDim.x) {
-        float acc = 0.f;
-        for (int s = 0; s < S; ++s) {
-#pragma unroll 4
-            for (int g = g_lo; g < g_hi; ++g) acc = fmaf(coef[g * S + s], po[((size_t)s * H + g) * G * Dv + d], acc);
+    for (int g = threadIdx.x; g < H; g += blockDim.x) {
+        float M = sink ? sink[g] : -INFINITY;
+        for (int s = 0; s < S; ++s) M = fmaxf(M, coef[s * H + g]);
+        float den = sink ? expf(sink[g] - M) : 0.f;
+        for (int s = 0; s < S; ++s) if (coef[s * H + g] > -INFINITY) den += pl_s[s * H + g] * expf(coef[s * H + g] - M);
+        M_s[g] = M;
+        inv_s[g] = den > 0.f ? 1.0f / den : 0.f;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < S * H; e += blockDim.x) {
+        const int g = e % H;
+        coef[e] = coef[e] > -INFINITY ? expf(coef[e] - M_s[g]) * inv_s[g] : 0.f;
+    }
+    __syncthreads();
+    const int R = blockDim.x / Dv, r = threadIdx.x / Dv, d = threadIdx.x % Dv;
+    const int h = share ? blockIdx.y : blockIdx.y * R + r;   // this group's head
+    const bool on = r < R && h < H;
+    float acc = 0.f;
+    if (on) {
+        const float* po = a.po + (size_t)t * S * H * G * Dv + (size_t)(h / per_kv) * Dv + d;
+        const float* mrow = mix ? mix + (size_t)h * H : nullptr;
+        const int first = share ? r : 0, step = share ? R : 1;
+        if (mix) {
+            // pairs (s, g) in the order s-major; g advances by `step` with carry into s (no division in the loop)
+            int sg = first / H, g = first % H;
+#pragma unroll 8
+            for (int p = first; p < S * H; p += step) {
+                acc = fmaf(coef[sg * H + g] * mrow[g], po[((size_t)sg * H + g) * G * Dv], acc);
+                g += step;
+                while (g >= H) { g -= H; ++sg; }
+            }
+        } else {
+#pragma unroll 8
+            for (int sg = first; sg < S; sg += step) acc = fmaf(coef[sg * H + h], po[((size_t)sg * H + h) * G * Dv], acc);
         }
-        out[((size_t)t * H + h) * Dv + d] = __float2bfloat16_rn(acc);
+    }
+    if (!share) {
+        if (on) out[((size_t)t * H + h) * Dv + d] = __float2bfloat16_rn(acc);
+        return;
+    }
+    if (on) red[r * Dv + d] = acc;
+    __syncthreads();
+    if (threadIdx.x < Dv) {
+        float sum = 0.f;
+        for (int k = 0; k < R; ++k) sum += red[k * Dv + threadIdx.x];
+        out[((size_t)t * H + blockIdx.y) * Dv + threadIdx.x] = __float2bfloat16_rn(sum);
     }
 }
 
@@ -335,7 +372,8 @@ extern "C" int pe_attention_flashmix(const void* q, int q_stride, void* out, con
     FlashMixArgs a = {(const bf16*)q, q_stride, (const bf16*)k_pool, (const bf16*)v_pool, table, table_stride, tok_pos, tok_row, tiles,
                       H, G, D, Dv, window, scale, splits, cg, ngroups, pm, pl, po};
     const size_t smem = 2 * 2 * ((size_t)PE_PAGE * (D + FX_PAD) + (size_t)cg * PE_PAGE * (Dv + FX_PAD));      // two stages of bfloat16
-    const size_t merge_smem = sizeof(float) * (size_t)H * splits;
+    const int merge_threads = Dv >= 256 ? Dv : (256 / Dv) * Dv;                    // whole groups of Dv threads
+    const size_t merge_smem = sizeof(float) * (2 * (size_t)H * splits + 2 * (size_t)H + (size_t)merge_threads);
     if (smem > 220 * 1024 || merge_smem > 48 * 1024 || H > 65535) return PE_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
     const dim3 grid(tiles ? n_runs : T, (tiles ? H : G) * ngroups, splits);
@@ -345,7 +383,10 @@ extern "C" int pe_attention_flashmix(const void* q, int q_stride, void* out, con
     else if (dk <= 8) rc = nv <= 16 ? fx_launch<8, 16>(a, grid, smem, s) : fx_launch<8, 32>(a, grid, smem, s);
     else rc = nv <= 16 ? fx_launch<16, 16>(a, grid, smem, s) : fx_launch<16, 32>(a, grid, smem, s);
     if (rc) return rc;
-    PE_TRY(pe_launch(flashmix_merge_kernel, dim3(T, H), Dv <= 64 ? 64 : (Dv <= 128 ? 128 : 256), merge_smem, s, a, sink, mix, (bf16*)out));
+    const int groups = merge_threads / Dv;
+    const int share = (splits * (mix ? H : 1) >= 64 && groups > 1) ? 1 : 0;          // many pairs to add: the groups share a head
+    PE_TRY(pe_launch(flashmix_merge_kernel, dim3(T, share ? H : (H + groups - 1) / groups), merge_threads, merge_smem, s, a, sink, mix,
+                     (bf16*)out, share));
     PE_LAUNCH_CHECK();
     return 0;
 }

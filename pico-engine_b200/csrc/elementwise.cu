@@ -544,10 +544,37 @@ __global__ void activation_kernel(const T* in, T* out, int kind, size_t total) {
     }
 }
 
+__device__ __forceinline__ float activation_of(float v, int kind) {
+    if (kind == 0) { const float p = fmaxf(v, 0.f); return p * p; }
+    if (kind == 1) return 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+    return v / (1.0f + expf(-v));
+}
+
+__global__ void activation_bf16x8_kernel(const bf16* in, bf16* out, int kind, size_t groups) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < groups; e += (size_t)gridDim.x * blockDim.x) {
+        uint4 v = *reinterpret_cast<const uint4*>(in + e * 8);
+        __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float2 f = __bfloat1622float2(p[k]);
+            p[k] = __floats2bfloat162_rn(activation_of(f.x, kind), activation_of(f.y, kind));
+        }
+        *reinterpret_cast<uint4*>(out + e * 8) = v;
+    }
+}
+
 extern "C" int pe_activation(const void* in, void* out, int dtype, int kind, long long total, void* stream) {
     if (total <= 0) return 0;
     if (kind < 0 || kind > 2) return PE_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == PE_BF16 && total % 8 == 0 && !(((uintptr_t)in | (uintptr_t)out) & 15)) {
+        const long long groups = total / 8, wantg = (groups + 255) / 256;
+        PE_TRY(pe_launch(activation_bf16x8_kernel, (int)(wantg < 148 * 16 ? wantg : 148 * 16), 256, 0, s, (const bf16*)in, (bf16*)out, kind, (size_t)groups));
+        PE_LAUNCH_CHECK();
+        return 0;
+    }
     const long long want = (total + 255) / 256;
     const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
     if (dtype == PE_F32) PE_TRY(pe_launch(activation_kernel<float>, blocks, 256, 0, s, (const float*)in, (float*)out, kind, (size_t)total));

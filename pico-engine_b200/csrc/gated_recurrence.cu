@@ -19,7 +19,7 @@
 //    of pass 3 would still read the old ones.
 #include "common.cuh"
 
-#define MG_CHUNK 32
+#define MG_CHUNK 16
 #define MG_THREADS 128
 
 __device__ __forceinline__ float sigmoid_f(float v) { return 1.0f / (1.0f + expf(-v)); }
@@ -54,6 +54,24 @@ __global__ void __launch_bounds__(MG_THREADS) mingru_sequential_kernel(const T* 
     *sp = S;
 }
 
+#define MG_BATCH 16     // tokens whose projections a thread loads before it walks them: the loads are in flight together
+
+template <typename T>
+__device__ __forceinline__ void mg_load(const T* proj, int t, int n, int W, int ch, float (&pz)[MG_BATCH], float (&pu)[MG_BATCH], float (&pg)[MG_BATCH]) {
+#pragma unroll
+    for (int k = 0; k < MG_BATCH; ++k) {
+        if (k < n) {
+            const T* row = proj + (size_t)(t + k) * 3 * W;
+            pz[k] = to_f(row[ch]); pu[k] = to_f(row[W + ch]); pg[k] = to_f(row[2 * (size_t)W + ch]);
+        }
+    }
+}
+__device__ __forceinline__ void mg_gate_values(float pz, float pu, float& a, float& zc) {
+    const float z = sigmoid_f(pz);
+    a = 1.0f - z;
+    zc = z * (pu >= 0.f ? pu + 0.5f : sigmoid_f(pu));
+}
+
 // pass 1: (A, B) of every chunk; `carry` [chunks, 2, W]
 template <typename T>
 __global__ void __launch_bounds__(MG_THREADS) mingru_chunk_kernel(const T* proj, const float* state, long long state_stride,
@@ -65,35 +83,49 @@ __global__ void __launch_bounds__(MG_THREADS) mingru_chunk_kernel(const T* proj,
     if (ch >= W) return;
     const int t0 = k * MG_CHUNK, t1 = min(Ttot, t0 + MG_CHUNK);
     float A = 1.f, Bv = 0.f;
-    for (int t = t0; t < t1; ++t) {
-        float a, zc, gate;
-        mg_gates(proj + (size_t)t * 3 * W, W, ch, a, zc, gate);
-        const int b = tok_row[t];
-        if (t == row_first[b]) {                         // restart from the sequence's stored state
-            const float s_in = state[(size_t)slots[b] * state_stride + ch];
-            snap[(size_t)b * W + ch] = s_in;
-            A = 0.f;
-            Bv = fmaf(a, s_in, zc);
-        } else {
-            A *= a;
-            Bv = fmaf(a, Bv, zc);
+    for (int tb = t0; tb < t1; tb += MG_BATCH) {
+        float pz[MG_BATCH], pu[MG_BATCH], pg[MG_BATCH];
+        const int n = min(MG_BATCH, t1 - tb);
+        mg_load(proj, tb, n, W, ch, pz, pu, pg);
+#pragma unroll
+        for (int j = 0; j < MG_BATCH; ++j) {
+            if (j < n) {
+                const int t = tb + j;
+                float a, zc;
+                mg_gate_values(pz[j], pu[j], a, zc);
+                const int b = tok_row[t];
+                if (t == row_first[b]) {                     // restart from the sequence's stored state
+                    const float s_in = state[(size_t)slots[b] * state_stride + ch];
+                    snap[(size_t)b * W + ch] = s_in;
+                    A = 0.f;
+                    Bv = fmaf(a, s_in, zc);
+                } else {
+                    A *= a;
+                    Bv = fmaf(a, Bv, zc);
+                }
+            }
         }
     }
     carry[((size_t)k * 2) * W + ch] = A;
     carry[((size_t)k * 2 + 1) * W + ch] = Bv;
 }
 
-// pass 2: carry[k][0] <- S_in of chunk k
+// pass 2: carry[k][0] <- S_in of chunk k (the pairs of 8 chunks are loaded before they are walked)
 __global__ void __launch_bounds__(MG_THREADS) mingru_carry_kernel(float* carry, int chunks, int W) {
     pdl_launch_dependents();
     pdl_wait();
     const int ch = blockIdx.x * MG_THREADS + threadIdx.x;
     if (ch >= W) return;
     float S = 0.f;
-    for (int k = 0; k < chunks; ++k) {
-        const float A = carry[((size_t)k * 2) * W + ch], Bv = carry[((size_t)k * 2 + 1) * W + ch];
-        carry[((size_t)k * 2) * W + ch] = S;
-        S = fmaf(A, S, Bv);
+    for (int kb = 0; kb < chunks; kb += MG_BATCH) {
+        float A[MG_BATCH], Bv[MG_BATCH];
+        const int n = min(MG_BATCH, chunks - kb);
+#pragma unroll
+        for (int j = 0; j < MG_BATCH; ++j)
+            if (j < n) { A[j] = carry[((size_t)(kb + j) * 2) * W + ch]; Bv[j] = carry[((size_t)(kb + j) * 2 + 1) * W + ch]; }
+#pragma unroll
+        for (int j = 0; j < MG_BATCH; ++j)
+            if (j < n) { carry[((size_t)(kb + j) * 2) * W + ch] = S; S = fmaf(A[j], S, Bv[j]); }
     }
 }
 
@@ -108,14 +140,23 @@ __global__ void __launch_bounds__(MG_THREADS) mingru_apply_kernel(const T* proj,
     if (ch >= W) return;
     const int t0 = k * MG_CHUNK, t1 = min(Ttot, t0 + MG_CHUNK);
     float S = carry[((size_t)k * 2) * W + ch];
-    for (int t = t0; t < t1; ++t) {
-        float a, zc, gate;
-        mg_gates(proj + (size_t)t * 3 * W, W, ch, a, zc, gate);
-        const int b = tok_row[t];
-        if (t == row_first[b]) S = snap[(size_t)b * W + ch];
-        S = fmaf(a, S, zc);
-        y[(size_t)t * W + ch] = from_f<T>(S * gate);
-        if (t + 1 == row_first[b + 1]) state[(size_t)slots[b] * state_stride + ch] = S;      // the sequence's last token of the step
+    for (int tb = t0; tb < t1; tb += MG_BATCH) {
+        float pz[MG_BATCH], pu[MG_BATCH], pg[MG_BATCH];
+        const int n = min(MG_BATCH, t1 - tb);
+        mg_load(proj, tb, n, W, ch, pz, pu, pg);
+#pragma unroll
+        for (int j = 0; j < MG_BATCH; ++j) {
+            if (j < n) {
+                const int t = tb + j;
+                float a, zc;
+                mg_gate_values(pz[j], pu[j], a, zc);
+                const int b = tok_row[t];
+                if (t == row_first[b]) S = snap[(size_t)b * W + ch];
+                S = fmaf(a, S, zc);
+                y[(size_t)t * W + ch] = from_f<T>(S * (pg[j] * sigmoid_f(pg[j])));
+                if (t + 1 == row_first[b + 1]) state[(size_t)slots[b] * state_stride + ch] = S;      // the sequence's last token of the step
+            }
+        }
     }
 }
 

@@ -116,9 +116,9 @@ extern "C" int pe_conv_state_update(const float* y, float* state, long long stat
 }
 
 // ---------------------------------------------------------------- both norms and both convolutions of a parallel block
-// One block per token.  The two norms of a parallel block read the same row, so its mean and variance are
-// computed once; the rows of the taps - 1 tokens before it are normed again here (they come from L2) rather
-// than written out in float32 and read back.  Half 2 is skipped when out2 is null.
+// The two norms of a parallel block read the same rows, so a row's mean and variance are computed once for both;
+// the rows of the taps - 1 tokens before a token are normed again where they are needed (they come from L1 or L2)
+// rather than written out in float32 and read back.  Half 2 is skipped when out2 is null.
 #define LC_MAX_TAPS 8
 
 struct NormConvHalf {
@@ -128,42 +128,133 @@ struct NormConvHalf {
     void* out;
 };
 
-template <typename TO>
+#define LC_TOKENS 8
+
+// mean and 1/sqrt(var + eps) of a row by one warp (two passes over the row, which stays in L1)
+__device__ __forceinline__ void warp_row_stats(const float* row, int H, float eps, float& mean, float& rstd) {
+    const int lane = threadIdx.x & 31;
+    float s = 0.f;
+    if ((H & 3) == 0) {
+        for (int i = lane * 4; i < H; i += 128) { const float4 v = *reinterpret_cast<const float4*>(row + i); s += (v.x + v.y) + (v.z + v.w); }
+    } else {
+        for (int i = lane; i < H; i += 32) s += row[i];
+    }
+    mean = warp_sum(s) / (float)H;
+    float q = 0.f;
+    if ((H & 3) == 0) {
+        for (int i = lane * 4; i < H; i += 128) {
+            const float4 v = *reinterpret_cast<const float4*>(row + i);
+            const float a = v.x - mean, b = v.y - mean, c = v.z - mean, d = v.w - mean;
+            q += (a * a + b * b) + (c * c + d * d);
+        }
+    } else {
+        for (int i = lane; i < H; i += 32) { const float d = row[i] - mean; q = fmaf(d, d, q); }
+    }
+    rstd = 1.0f / sqrtf(warp_sum(q) / (float)H + eps);
+}
+
+// A block takes `tpb` (up to LC_TOKENS) consecutive packed tokens.  First a warp per row computes the statistics of the
+// block's rows and of the taps - 1 rows before them; then a thread keeps the norm weights and taps of its channels in
+// registers and walks the block's tokens, the normed values of the taps - 1 tokens before in a sliding window of
+// registers (a token whose sequence starts later than the window reaches takes those values from the state instead).
+// NC channels a thread at a time: 4 (16-byte loads of x) where H is a multiple of 4, else 1.
+template <typename TO, int NC, int MT>        // MT: the most taps this instance takes (registers of the window and the taps)
 __global__ void __launch_bounds__(LN_THREADS) dual_layernorm_conv_kernel(
     const float* x, NormConvHalf h1, NormConvHalf h2, long long state_stride, const int* tok_row, const int* row_first,
-    const int* slots, float eps, int H, int taps, int update_state) {
+    const int* slots, float eps, int T, int H, int taps, int tpb, int update_state) {
     pdl_launch_dependents();
     pdl_wait();
-    __shared__ float scratch[33];
-    const int t = blockIdx.x;
-    const int b = tok_row[t], i = t - row_first[b];
-    const int inside = min(i, taps - 1);                 // how many of the earlier tokens are rows of this step
-    float mean[LC_MAX_TAPS], rstd[LC_MAX_TAPS];
-    for (int back = 0; back <= inside; ++back)
-        row_stats(x + (size_t)(t - back) * H, H, eps, scratch, mean[back], rstd[back]);
-    const size_t slot_off = (size_t)slots[b] * state_stride;
+    __shared__ float mean_s[LC_TOKENS + LC_MAX_TAPS], rstd_s[LC_TOKENS + LC_MAX_TAPS];
+    __shared__ int idx_s[LC_TOKENS];                       // index of each token within its sequence's tokens of this step
+    __shared__ long long slot_s[LC_TOKENS];
+    const int t0 = blockIdx.x * tpb, n_tok = min(tpb, T - t0);
+    const int warp = threadIdx.x >> 5, halo = taps - 1;
+    for (int r = warp; r < n_tok + halo; r += LN_THREADS / 32) {      // row r stands for token t0 - halo + r
+        const int t = t0 - halo + r;
+        if (t >= 0) {
+            float mean, rstd;
+            warp_row_stats(x + (size_t)t * H, H, eps, mean, rstd);
+            if ((threadIdx.x & 31) == 0) { mean_s[r] = mean; rstd_s[r] = rstd; }
+        }
+    }
+    if (threadIdx.x < n_tok) {
+        const int b = tok_row[t0 + threadIdx.x];
+        idx_s[threadIdx.x] = t0 + threadIdx.x - row_first[b];
+        slot_s[threadIdx.x] = (long long)slots[b] * state_stride;
+    }
+    __syncthreads();
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
         const NormConvHalf& hh = half ? h2 : h1;
         if (hh.out == nullptr) continue;
-        float* st = hh.state + slot_off;
-        TO* o = (TO*)hh.out + (size_t)t * H;
-        for (int ch = threadIdx.x; ch < H; ch += blockDim.x) {
-            const float w = load_as_f(hh.w, hh.w_dtype, ch), bb = load_as_f(hh.b, hh.b_dtype, ch);
-            const float own = (x[(size_t)t * H + ch] - mean[0]) * rstd[0] * w + bb;
-            float acc = own;
-            for (int j = 0; j < taps; ++j) {
-                const int back = taps - 1 - j;
-                float v;
-                if (back == 0) v = own;
-                else if (back <= inside) v = (x[(size_t)(t - back) * H + ch] - mean[back]) * rstd[back] * w + bb;
-                else v = st[(size_t)(back - i - 1) * H + ch];
-                acc = fmaf(load_as_f(hh.c, hh.c_dtype, (size_t)ch * taps + j), v, acc);
+        for (int ch = threadIdx.x * NC; ch < H; ch += LN_THREADS * NC) {
+            float w[NC], bb[NC], c[MT][NC], win[MT][NC];      // win[d]: the normed value d + 1 tokens back
+#pragma unroll
+            for (int u = 0; u < NC; ++u) {
+                w[u] = load_as_f(hh.w, hh.w_dtype, ch + u); bb[u] = load_as_f(hh.b, hh.b_dtype, ch + u);
+#pragma unroll
+                for (int d = 0; d < MT; ++d)        // c[d]: the tap that meets the token d places back
+                    c[d][u] = d < taps ? load_as_f(hh.c, hh.c_dtype, (size_t)(ch + u) * taps + (taps - 1 - d)) : 0.f;
             }
-            o[ch] = from_f<TO>(acc);
-            if (update_state) {                          // the sequence brings this one token: shift its entries, newest first
-                for (int k = taps - 2; k > 0; --k) st[(size_t)k * H + ch] = st[(size_t)(k - 1) * H + ch];
-                if (taps > 1) st[ch] = own;
+#pragma unroll
+            for (int d = 0; d < MT; ++d) {
+                const int t = t0 - 1 - d;
+                float xv[NC];
+#pragma unroll
+                for (int u = 0; u < NC; ++u) xv[u] = 0.f;
+                if (d < halo && t >= 0) {
+                    if (NC == 4) { const float4 v = *reinterpret_cast<const float4*>(x + (size_t)t * H + ch); xv[0] = v.x; xv[1 % NC] = v.y; xv[2 % NC] = v.z; xv[3 % NC] = v.w; }
+                    else xv[0] = x[(size_t)t * H + ch];
+                }
+#pragma unroll
+                for (int u = 0; u < NC; ++u)
+                    win[d][u] = (d < halo && t >= 0) ? (xv[u] - mean_s[halo - 1 - d]) * rstd_s[halo - 1 - d] * w[u] + bb[u] : 0.f;
+            }
+            for (int k = 0; k < n_tok; ++k) {
+                const int t = t0 + k, i = idx_s[k];
+                float* st = hh.state + slot_s[k];
+                float xv[NC], own[NC], acc[NC];
+                if (NC == 4) { const float4 v = *reinterpret_cast<const float4*>(x + (size_t)t * H + ch); xv[0] = v.x; xv[1 % NC] = v.y; xv[2 % NC] = v.z; xv[3 % NC] = v.w; }
+                else xv[0] = x[(size_t)t * H + ch];
+#pragma unroll
+                for (int u = 0; u < NC; ++u) { own[u] = (xv[u] - mean_s[k + halo]) * rstd_s[k + halo] * w[u] + bb[u]; acc[u] = own[u]; }
+#pragma unroll
+                for (int u = 0; u < NC; ++u) acc[u] = fmaf(c[0][u], own[u], acc[u]);
+#pragma unroll
+                for (int back = 1; back < MT; ++back) {
+                    if (back < taps) {
+#pragma unroll
+                        for (int u = 0; u < NC; ++u) {
+                            const float v = back <= i ? win[back - 1][u] : st[(size_t)(back - i - 1) * H + ch + u];
+                            acc[u] = fmaf(c[back][u], v, acc[u]);
+                        }
+                    }
+                }
+                TO* o = (TO*)hh.out + (size_t)t * H + ch;
+                if (NC == 4 && sizeof(TO) == 2) {            // four bfloat16 as one 8-byte store
+                    const __nv_bfloat162 lo2 = __floats2bfloat162_rn(acc[0], acc[1 % NC]), hi2 = __floats2bfloat162_rn(acc[2 % NC], acc[3 % NC]);
+                    uint2 pk;
+                    pk.x = *reinterpret_cast<const uint32_t*>(&lo2); pk.y = *reinterpret_cast<const uint32_t*>(&hi2);
+                    *reinterpret_cast<uint2*>(o) = pk;
+                } else if (NC == 4) {
+                    *reinterpret_cast<float4*>(o) = make_float4(acc[0], acc[1 % NC], acc[2 % NC], acc[3 % NC]);
+                } else {
+                    o[0] = from_f<TO>(acc[0]);
+                }
+                if (update_state) {                          // the sequence brings this one token: shift its entries, newest first
+#pragma unroll
+                    for (int u = 0; u < NC; ++u) {
+                        for (int e = taps - 2; e > 0; --e) st[(size_t)e * H + ch + u] = st[(size_t)(e - 1) * H + ch + u];
+                        if (taps > 1) st[ch + u] = own[u];
+                    }
+                }
+#pragma unroll
+                for (int d = MT - 1; d > 0; --d) {
+#pragma unroll
+                    for (int u = 0; u < NC; ++u) win[d][u] = win[d - 1][u];
+                }
+#pragma unroll
+                for (int u = 0; u < NC; ++u) win[0][u] = own[u];
             }
         }
     }
@@ -205,9 +296,21 @@ extern "C" int pe_dual_layernorm_conv(const float* x, const void* w1, int w1_dty
     NormConvHalf h1 = {w1, b1, c1, w1_dtype, b1_dtype, c1_dtype, state1, out1};
     NormConvHalf h2 = {w2, b2, c2, w2_dtype, b2_dtype, c2_dtype, state2, out2};
     const int inline_update = one_token_each ? 1 : 0;
-    if (out_dtype == PE_F32) PE_TRY(pe_launch(dual_layernorm_conv_kernel<float>, T, LN_THREADS, 0, s, x, h1, h2, state_stride, tok_row, row_first, slots, eps, H, taps, inline_update));
-    else if (out_dtype == PE_BF16) PE_TRY(pe_launch(dual_layernorm_conv_kernel<bf16>, T, LN_THREADS, 0, s, x, h1, h2, state_stride, tok_row, row_first, slots, eps, H, taps, inline_update));
-    else return PE_ERR_UNSUPPORTED;
+    // tokens a block: as many as leave a few blocks for every SM
+    int tpb = LC_TOKENS;
+    while (tpb > 1 && (T + tpb - 1) / tpb < 148) tpb >>= 1;
+    const int blocks = (T + tpb - 1) / tpb;
+    const bool vec = (H & 3) == 0 && !(((uintptr_t)x | (uintptr_t)out1 | (uintptr_t)out2) & 15);
+#define LC_LAUNCH(TO, NC, MT) PE_TRY(pe_launch(dual_layernorm_conv_kernel<TO, NC, MT>, blocks, LN_THREADS, 0, s, x, h1, h2, state_stride, \
+                                               tok_row, row_first, slots, eps, T, H, taps, tpb, inline_update))
+    if (out_dtype == PE_F32) {
+        if (vec) { if (taps <= 4) LC_LAUNCH(float, 4, 4); else LC_LAUNCH(float, 4, LC_MAX_TAPS); }
+        else { if (taps <= 4) LC_LAUNCH(float, 1, 4); else LC_LAUNCH(float, 1, LC_MAX_TAPS); }
+    } else if (out_dtype == PE_BF16) {
+        if (vec) { if (taps <= 4) LC_LAUNCH(bf16, 4, 4); else LC_LAUNCH(bf16, 4, LC_MAX_TAPS); }
+        else { if (taps <= 4) LC_LAUNCH(bf16, 1, 4); else LC_LAUNCH(bf16, 1, LC_MAX_TAPS); }
+    }
+#undef LC_LAUNCH
     PE_LAUNCH_CHECK();
     if (!inline_update && taps > 1) {
         PE_TRY(pe_launch(dual_layernorm_state_kernel, B, LN_THREADS, 0, s, x, h1, h2, state_stride, row_first, row_lens, slots, eps, H, taps));

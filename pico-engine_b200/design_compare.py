@@ -25,11 +25,9 @@ TAPS = 4
 
 
 def mebalorn_config(size: str) -> dict:
+    from .config.shapes import mebalorn_shape
     W, H, G, D, F, L = SIZES[size]
-    att = {"type": "attention", "mixer": {"heads": H, "kv_heads": G, "dim": D, "vdim": D, "scale": D ** -0.5}, "mlp": {"kind": "dense", "ff": F}}
-    rec = {"type": "mingru", "mixer": {"width": W}, "mlp": {"kind": "dense", "ff": F}}
-    return {"architecture": "Mebalorn", "vocab": VOCAB, "width": W, "canon": {"taps": TAPS}, "norm": {"eps": 1e-6},
-            "logit_softcap": 30.0, "layers": [rec if i % 2 == 0 else att for i in range(L)]}
+    return mebalorn_shape(W, H, G, D, F, L, VOCAB, taps=TAPS)
 
 
 def qwen2_config(size: str) -> dict:

@@ -849,10 +849,12 @@ def attention_headmix(q: torch.Tensor, q_stride: int, n_heads: int, n_kv: int, h
         if cg and q_stride % 2 == 0:
             # one pass over the keys with an output for every (head, value head), then merge + sink + mixing
             blocks = (n_runs * n_heads if tiles is not None else T * n_kv) * ((n_kv + cg - 1) // cg)
-            # enough blocks to fill the GPU; long prompts are cut too, so that the last rows' blocks (which see the most
-            # keys) do not run on after all others have ended
-            splits = max(1, min((ctx.max_context + 1023) // 1024, 8)) if blocks >= 296 else \
-                max(1, min((296 + blocks - 1) // blocks, (ctx.max_context + 127) // 128, 64))
+            # Few blocks (single tokens with long contexts): the keys are cut into ranges until about one and a half blocks
+            # an SM run.  Measured on a B200 (8 tokens at 2,048 keys): 14 heads of 64 on 2 key/value heads 65 / 47 / 29 / 32 /
+            # 51 us at 2 / 4 / 8 / 16 / 32 ranges, 16 heads of 128 on 4 key/value heads 82 / 55 / 70 / 97 / 202 us: more ranges
+            # mean more partial outputs to write and merge.  A prompt has blocks enough and is not cut (2,048 tokens: 183 us
+            # uncut, 209 us in two ranges).
+            splits = max(1, min((224 + blocks - 1) // blocks, (ctx.max_context + 63) // 64, 64))
             ws = scratch("attention_headmix", 4 * lib.pe_attention_flashmix_scratch_floats(T, splits, n_heads, n_kv, v_head_dim), q.device)
             check(lib.pe_attention_flashmix(q.data_ptr(), q_stride, out.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(),
                                             block_table.data_ptr(), table_stride, tok_pos.data_ptr(), tok_row.data_ptr(), _ptr(tiles),

@@ -61,7 +61,9 @@ def test_named_shapes_are_valid_configurations():
     from pico_engine.config.shapes import SHAPES, shape
     for name in SHAPES:
         cfg = config_from_dict(shape(name))
-        assert cfg.plan().layers and cfg.num_attention_heads % cfg.num_key_value_heads == 0
+        assert cfg.plan().layers
+        if hasattr(cfg, "num_attention_heads"):
+            assert cfg.num_attention_heads % cfg.num_key_value_heads == 0
     b = json.load(open(os.path.join(ROOT, "BASELINE.json")))["configs"][2]
     c = config_from_dict(shape("qwen2.5-0.5b"))
     for word in ("24 layers", "hidden 896", "14 heads", "2 KV heads", "head_dim 64", "intermediate 4864", "vocab 151936"):
