@@ -38,6 +38,10 @@ CONFIGS = {
     "M3": config(200, 40, 2, 3e-6, 30.0, [attention(2, 1, 24, 40, 0.2, 56), mingru(24, 72), attention(2, 2, 40, 8, 0.17, 48)]),
     # five taps, recurrence only
     "M4": config(96, 56, 5, 1e-5, 5.0, [mingru(64, 80), mingru(56, None)]),
+    # many heads (beyond what the tensor-core kernels take), head sizes that are no multiples of 8, eight taps, a wide state
+    "M5": config(150, 100, 8, 1e-6, 12.0, [attention(40, 8, 20, 12, 0.22, 72), mingru(520, 40)]),
+    # nine taps (more than the fused norm + convolution kernel takes), key and value sizes 80 and 48, a width that is no multiple of 4
+    "M6": config(90, 50, 9, 2e-6, None, [mingru(30, None), attention(6, 3, 80, 48, 0.11, 60)]),
 }
 
 

@@ -19,7 +19,8 @@ pytestmark = pytest.mark.gpu
 
 DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16}
 CASES = [(n, d) for n in sorted(CONFIGS) for d in ("float32", "bfloat16")]
-LENGTHS = {"M1": [1, 2, 3, 37, 70, 131, 64, 5], "M2": [65, 1, 130, 9, 33, 2], "M3": [3, 129, 31, 32, 64, 1, 200], "M4": [4, 1, 90, 17, 5]}
+LENGTHS = {"M1": [1, 2, 3, 37, 70, 131, 64, 5], "M2": [65, 1, 130, 9, 33, 2], "M3": [3, 129, 31, 32, 64, 1, 200], "M4": [4, 1, 90, 17, 5],
+           "M5": [70, 2, 11, 33], "M6": [12, 1, 66, 9, 40]}
 
 
 @pytest.fixture(scope="module")
