@@ -60,9 +60,20 @@ def config_from_dict(config_dict: dict):
 
 
 def read_config(folder: str):
-    """The typed configuration of the model folder ``folder`` (its config.json)."""
+    """The typed configuration of the model folder ``folder`` (its config.json).  A configuration class that sets
+    ``READS_TENSOR_SHAPES`` has sizes that only the stored tensors give: its ``from_dict`` also gets the shapes of the
+    folder's checkpoint, name -> shape (None where the folder has no weights)."""
     path = os.path.join(folder, "config.json")
     if not os.path.isfile(path):
         raise ConfigError(f"no config.json in {folder!r}")
     with open(path, "r", encoding="utf-8") as f:
-        return config_from_dict(json.load(f))
+        d = json.load(f)
+    cls = architecture(architecture_name_of(d)).config_class
+    if getattr(cls, "READS_TENSOR_SHAPES", False):
+        from ..weights.safetensors_io import Checkpoint, SafetensorsError
+        try:
+            shapes = {n: tuple(e.shape) for n, e in Checkpoint(folder).entries.items()}
+        except (OSError, SafetensorsError):
+            shapes = None
+        return cls.from_dict(d, shapes)
+    return cls.from_dict(d)

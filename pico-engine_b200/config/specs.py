@@ -31,6 +31,7 @@ class RMSNormSpec(PartSpec):
     size: int
     eps: float
     weight: str                      # tensor name
+    one_plus: bool = False           # the stored vector lies around zero and the norm multiplies by 1 + it
 
 
 @dataclass(frozen=True)
@@ -55,6 +56,17 @@ class RotaryHalfSpec(PartSpec):
 @dataclass(frozen=True)
 class NoPositionSpec(PartSpec):
     """Queries and keys are used as projected."""
+
+
+@dataclass(frozen=True)
+class RotaryPairsSpec(PartSpec):
+    """Rotary encoding of neighbouring entries: (2i, 2i+1) of the first ``dims`` entries of a head are turned by the
+    angle pos * base^(-2i/dims) / factor (``factor`` > 1 stretches positions linearly); the other entries of the
+    head stay as they are."""
+    head_dim: int
+    dims: int
+    base: float
+    factor: float = 1.0
 
 
 @dataclass(frozen=True)
@@ -149,6 +161,77 @@ class MinGRUSpec(PartSpec):
     bias_suffix: str = ".b"
 
 
+@dataclass(frozen=True)
+class GatedAttentionSpec(PartSpec):
+    """Softmax attention with grouped key/value heads whose concatenated heads are multiplied by a gate of the
+    mixer's own input before the output projection: o <- o * sigmoid(W_g h) (``gate`` None: no gate).  ``position``
+    acts on queries and keys; with ``qk_unit_norm`` every query and key head is then divided by its root mean square
+    (eps ``norm_eps``, no weight).  Keys and values may have different head sizes; ``window`` as in
+    :class:`GQAAttentionSpec`.  No biases.  Tensor names are ``prefix + name``."""
+    hidden: int
+    n_heads: int
+    n_kv_heads: int
+    head_dim: int
+    v_head_dim: int
+    window: Optional[int]
+    scale: float
+    position: PartSpec
+    prefix: str
+    qk_unit_norm: bool = False
+    norm_eps: float = 1e-6
+    gate: Optional[str] = "g"
+    q_name: str = "q"
+    k_name: str = "k"
+    v_name: str = "v"
+    o_name: str = "o"
+
+
+@dataclass(frozen=True)
+class LinearAttentionSpec(PartSpec):
+    """Attention without a softmax, as a recurrence over a matrix state per head:
+    S_t = diag(a_t) S_(t-1) + k_t v_t^T, o_t = S_t^T q_t, S [head_dim, v_head_dim] float32, zero at a sequence's start.
+
+    The decay a_t is either fixed, one number per head (``head_decay``), or learned per key channel and token:
+    a = sigmoid(W_2 (W_1 h) + b)^(1/decay_tau) with the low-rank pair ``decay_names`` = (W_1, W_2, b) of rank
+    ``decay_rank``.  ``qk_activation`` / ``v_activation`` ("none" or "silu") act on the projections, queries are
+    multiplied by ``q_scale``.  The output is normed (RMS, eps ``norm_eps``, plain weight ``norm_name``) over all heads
+    together (``norm_over`` "heads": weight of n_heads * v_head_dim) or head by head (``"head"``: one weight of
+    v_head_dim for all heads), multiplied by ``gate_activation`` ("sigmoid" or "silu") of W_g h, and projected by W_o."""
+    hidden: int
+    n_heads: int
+    head_dim: int
+    v_head_dim: int
+    prefix: str
+    head_decay: Optional[Tuple[float, ...]] = None
+    decay_names: Optional[Tuple[str, str, str]] = None
+    decay_rank: int = 0
+    decay_tau: float = 1.0
+    qk_activation: str = "none"
+    v_activation: str = "none"
+    q_scale: float = 1.0
+    norm_over: str = "heads"
+    norm_eps: float = 1e-6
+    norm_name: str = "norm"
+    gate_activation: str = "sigmoid"
+    q_name: str = "q"
+    k_name: str = "k"
+    v_name: str = "v"
+    g_name: str = "g"
+    o_name: str = "o"
+
+
+@dataclass(frozen=True)
+class BranchSumSpec(PartSpec):
+    """Several mixers side by side on the same input: the result is ``weight`` * sum_i rmsnorm(branch_i(h)) * w_i, each
+    branch's output normed over the model width (eps ``norm_eps``) with its own plain weight ``out_norms[i]``.  At most
+    one branch may keep keys and values; the branches' states lie one behind the other."""
+    hidden: int
+    branches: Tuple[PartSpec, ...]
+    out_norms: Tuple[str, ...]
+    norm_eps: float
+    weight: float = 0.5
+
+
 # ------------------------------------------------------------------ feed-forwards
 
 @dataclass(frozen=True)
@@ -173,6 +256,40 @@ class DenseMLPSpec(PartSpec):
     down_name: str = "down"
 
 
+@dataclass(frozen=True)
+class GatedMLPSpec(PartSpec):
+    """down(act(gate(x)) * up(x)), no biases; ``activation`` "gelu_tanh" or "silu".  Tensor names are ``prefix + name``."""
+    hidden: int
+    intermediate: int
+    prefix: str
+    activation: str = "silu"
+    gate_name: str = "gate"
+    up_name: str = "up"
+    down_name: str = "down"
+
+
+@dataclass(frozen=True)
+class MixtureSpec(PartSpec):
+    """``n_experts`` gated feed-forwards (``prefix + expert_name.format(e) + "." + gate/up/down``) of which a token uses
+    the ``top_k`` with the largest router logits (``prefix + router_name`` [n_experts, hidden], float32), weighted by the
+    softmax over the chosen logits alone.  ``shared_intermediate`` not None: one more expert (``prefix + shared_name``)
+    runs for every token and is added, multiplied by sigmoid(w_sg . h) (``shared_gate_name`` [1, hidden])."""
+    hidden: int
+    n_experts: int
+    top_k: int
+    intermediate: int
+    prefix: str
+    activation: str = "silu"
+    shared_intermediate: Optional[int] = None
+    router_name: str = "router"
+    expert_name: str = "e{}"
+    shared_name: str = "shared"
+    shared_gate_name: str = "shared.sg"
+    gate_name: str = "gate"
+    up_name: str = "up"
+    down_name: str = "down"
+
+
 # ------------------------------------------------------------------ layers and the model
 
 @dataclass(frozen=True)
@@ -193,6 +310,7 @@ class LayerSpec:
     arrangement: str = "pre_norm"
     mixer_input: Optional[PartSpec] = None           # applied to norm(x) before the mixer reads it (a CausalConvAddSpec)
     feed_forward_input: Optional[PartSpec] = None    # the same for the feed-forward
+    residual_scale: float = 1.0                      # x += residual_scale * sublayer(norm(x))
 
 
 @dataclass(frozen=True)
@@ -201,6 +319,8 @@ class ScheduleEntry:
     names an earlier entry of the schedule, whose cache it then reads without writing."""
     layer: int
     cache_of: Optional[int] = None
+    add_embedding: bool = False                      # before this execution, the embedded tokens are added to the stream again
+    add_vector: Optional[Tuple[str, int]] = None     # before this execution (and after the line above), row r of tensor "name" is added: (name, r)
 
 
 @dataclass(frozen=True)
@@ -218,6 +338,7 @@ class ModelPlan:
     ignorable_tensors: Tuple[str, ...] = field(default_factory=tuple)   # names a checkpoint may carry unused
     embedding_position: Optional[PartSpec] = None    # added to the embedding by position (a SinusoidAddSpec); None: nothing
     logit_softcap: Optional[float] = None            # logits <- cap * tanh(logits / cap); None: logits as projected
+    stream_vectors: Tuple[Tuple[str, int], ...] = ()  # (tensor name, rows): [rows, hidden] tensors whose rows schedule entries add to the stream
 
     def validate(self) -> None:
         if not self.layers:
@@ -225,6 +346,10 @@ class ModelPlan:
         for e, entry in enumerate(self.schedule):
             if not 0 <= entry.layer < len(self.layers):
                 raise ConfigError(f"schedule[{e}] names layer {entry.layer}, but there are {len(self.layers)} layers")
+            if entry.add_vector is not None:
+                rows = dict(self.stream_vectors).get(entry.add_vector[0])
+                if rows is None or not 0 <= entry.add_vector[1] < rows:
+                    raise ConfigError(f"schedule[{e}].add_vector={entry.add_vector} names no row of stream_vectors")
             if entry.cache_of is not None:
                 if not 0 <= entry.cache_of < e:
                     raise ConfigError(f"schedule[{e}].cache_of={entry.cache_of} must name an earlier entry")

@@ -1,0 +1,304 @@
+// Small kernels around gated mixers and routed feed-forwards: rotation of neighbouring pairs with a unit norm of
+// every head and the cache write; a norm over groups of channels times a gate; the sum of several normed
+// branches into the residual stream; a scaled residual sum; vectors added to the stream; a gated activation
+// with a weight per group of columns; the choice of experts.
+#include "common.cuh"
+
+extern "C" void pe_set_pdl(int on) { pe_pdl_enabled() = on ? 1 : 0; }     // (this library's own copy of the switch)
+
+__device__ __forceinline__ float go_sigmoid(float v) { return 1.0f / (1.0f + expf(-v)); }
+__device__ __forceinline__ float go_gelu_tanh(float v) {
+    return 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+}
+// activations: 0 none, 1 sigmoid, 2 silu, 3 gelu (tanh form)
+__device__ __forceinline__ float go_act(float v, int act) {
+    return act == 1 ? go_sigmoid(v) : act == 2 ? v * go_sigmoid(v) : act == 3 ? go_gelu_tanh(v) : v;
+}
+
+// ---------------------------------------------------------------- rotation of pairs, unit norm, cache write
+// qkv [T, ld] in the step's dtype, a row = H*D query | G*D key | G*Dv value entries (| whatever else the product made).  In every query and key head the entries (2i, 2i+1), 2i+1 < rot_dims,
+// are turned by the angle pos * freq[i]: (u, v) -> (u cos - v sin, v cos + u sin); then (norm != 0) the head is divided
+// by sqrt(mean(head^2) + eps).  The heads are rewritten in place; keys and values also go to their cache pages.
+// A warp a head; a lane keeps its entries of the head in registers (D <= 256).
+template <typename T>
+__global__ void __launch_bounds__(128) rotary_norm_store_kernel(T* qkv, int ld, int H, int G, int D, int Dv, const float* freq, int rot_dims,
+                                                                int norm, float eps, const int* tok_pos, const int* tok_row,
+                                                                T* k_pool, T* v_pool, const int* table, int table_stride, int store) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    T* row = qkv + (size_t)t * ld;
+    const int pos = tok_pos[t];
+    long long page = -1;
+    if (store) page = table[(size_t)tok_row[t] * table_stride + pos / PE_PAGE];
+    for (int u = warp; u < H + 2 * G; u += 4) {
+        if (u < H + G) {
+            T* v = row + (size_t)u * D;
+            float val[8];
+            float ss = 0.f;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const int d = lane + 32 * e;
+                float f = 0.f;
+                if (d < D) {
+                    f = to_f(v[d]);
+                    if ((d | 1) < rot_dims) {
+                        float sn, cs;
+                        sincosf((float)pos * freq[d >> 1], &sn, &cs);
+                        const float other = to_f(v[d ^ 1]);
+                        f = (d & 1) ? fmaf(f, cs, other * sn) : fmaf(f, cs, -other * sn);
+                    }
+                }
+                val[e] = f;
+                ss = fmaf(f, f, ss);
+            }
+            const float rstd = norm ? 1.0f / sqrtf(warp_sum(ss) / (float)D + eps) : 1.0f;
+            __syncwarp();                                                  // every lane has read its partners
+            T* dst = (u >= H && store && page >= 0) ? k_pool + (((size_t)page * G + (u - H)) * PE_PAGE + pos % PE_PAGE) * D : nullptr;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const int d = lane + 32 * e;
+                if (d < D) {
+                    const T o = from_f<T>(val[e] * rstd);
+                    v[d] = o;
+                    if (dst) dst[d] = o;
+                }
+            }
+        } else if (store && page >= 0) {
+            const int c = u - H - G;
+            const T* v = row + (size_t)(H + G) * D + (size_t)c * Dv;
+            T* dst = v_pool + (((size_t)page * G + c) * PE_PAGE + pos % PE_PAGE) * Dv;
+            for (int d = lane; d < Dv; d += 32) dst[d] = v[d];
+        }
+    }
+}
+
+extern "C" int pe_rotary_norm_store(void* qkv, int dtype, int ld, int T, int H, int G, int D, int Dv, const float* freq, int rot_dims,
+                                    int norm, float eps, const int* tok_pos, const int* tok_row, void* k_pool, void* v_pool,
+                                    const int* table, int table_stride, int store, void* stream) {
+    if (T <= 0) return 0;
+    if (D > 256 || rot_dims > D || (rot_dims & 1) || (rot_dims > 0 && !freq) || ld < (H + G) * D + G * Dv) return PE_ERR_UNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == PE_F32)
+        PE_TRY(pe_launch(rotary_norm_store_kernel<float>, T, 128, 0, s, (float*)qkv, ld, H, G, D, Dv, freq, rot_dims, norm, eps, tok_pos,
+                         tok_row, (float*)k_pool, (float*)v_pool, table, table_stride, store));
+    else if (dtype == PE_BF16)
+        PE_TRY(pe_launch(rotary_norm_store_kernel<bf16>, T, 128, 0, s, (bf16*)qkv, ld, H, G, D, Dv, freq, rot_dims, norm, eps, tok_pos,
+                         tok_row, (bf16*)k_pool, (bf16*)v_pool, table, table_stride, store));
+    else return PE_ERR_UNSUPPORTED;
+    PE_LAUNCH_CHECK();
+    return 0;
+}
+
+// ---------------------------------------------------------------- norm over groups of channels, times a gate
+// in [T, C] (float32 or the step's dtype); group > 0: every run of `group` channels is divided by
+// sqrt(mean(run^2) + eps) and multiplied by weight[channel % group]; then (gate != null) by act(gate[t, g_off + c]) of
+// gate [T, g_ld].  out [T, C] in the step's dtype.  A block a (token, group).
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(256) gated_norm_kernel(const TI* in, int C, int group, const void* weight, int w_dtype, float eps,
+                                                         const TO* gate, int g_ld, int g_off, int gate_act, TO* out) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float red[33];
+    const int t = blockIdx.x, n = group > 0 ? group : C, c0 = blockIdx.y * n;
+    const TI* src = in + (size_t)t * C + c0;
+    float rstd = 1.f;
+    if (group > 0) {
+        float ss = 0.f;
+        for (int i = threadIdx.x; i < n; i += blockDim.x) { const float f = to_f(src[i]); ss = fmaf(f, f, ss); }
+        rstd = 1.0f / sqrtf(block_sum(ss, red) / (float)n + eps);
+    }
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        float f = to_f(src[i]) * rstd;
+        if (group > 0 && weight) f *= load_as_f(weight, w_dtype, i);
+        if (gate) f *= go_act(to_f(gate[(size_t)t * g_ld + g_off + c0 + i]), gate_act);
+        out[(size_t)t * C + c0 + i] = from_f<TO>(f);
+    }
+}
+
+extern "C" int pe_gated_norm(const void* in, int in_dtype, int T, int C, int group, const void* weight, int w_dtype, float eps,
+                             const void* gate, int g_ld, int g_off, int gate_act, void* out, int out_dtype, void* stream) {
+    if (T <= 0 || C <= 0) return 0;
+    if (group < 0 || (group > 0 && C % group)) return PE_ERR_UNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int n = group > 0 ? group : C;
+    const dim3 grid(T, C / n);
+    const int threads = n >= 256 ? 256 : ((n + 31) / 32) * 32;
+    if (in_dtype == PE_F32 && out_dtype == PE_F32)
+        PE_TRY(pe_launch(gated_norm_kernel<float, float>, grid, threads, 0, s, (const float*)in, C, group, weight, w_dtype, eps,
+                         (const float*)gate, g_ld, g_off, gate_act, (float*)out));
+    else if (in_dtype == PE_F32 && out_dtype == PE_BF16)
+        PE_TRY(pe_launch(gated_norm_kernel<float, bf16>, grid, threads, 0, s, (const float*)in, C, group, weight, w_dtype, eps,
+                         (const bf16*)gate, g_ld, g_off, gate_act, (bf16*)out));
+    else if (in_dtype == PE_BF16 && out_dtype == PE_BF16)
+        PE_TRY(pe_launch(gated_norm_kernel<bf16, bf16>, grid, threads, 0, s, (const bf16*)in, C, group, weight, w_dtype, eps,
+                         (const bf16*)gate, g_ld, g_off, gate_act, (bf16*)out));
+    else return PE_ERR_UNSUPPORTED;
+    PE_LAUNCH_CHECK();
+    return 0;
+}
+
+// ---------------------------------------------------------------- x += scale * sum_i rmsnorm(y_i) * w_i
+// x [T, W] float32; up to 4 branches y_i [T, W] (all of one dtype) with plain weights w_i [W] (all of one dtype).
+struct NormedSumArgs { const void* y[4]; const void* w[4]; int n; };
+
+template <typename T>
+__global__ void __launch_bounds__(256) normed_sum_add_kernel(float* x, NormedSumArgs a, int w_dtype, int W, float eps, float scale) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float red[33];
+    const size_t t = blockIdx.x;
+    float rstd[4];
+    for (int b = 0; b < a.n; ++b) {
+        const T* y = (const T*)a.y[b] + t * W;
+        float ss = 0.f;
+        for (int i = threadIdx.x; i < W; i += blockDim.x) { const float f = to_f(y[i]); ss = fmaf(f, f, ss); }
+        rstd[b] = 1.0f / sqrtf(block_sum(ss, red) / (float)W + eps);
+    }
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+        float sum = 0.f;
+        for (int b = 0; b < a.n; ++b) sum += to_f(((const T*)a.y[b])[t * W + i]) * rstd[b] * load_as_f(a.w[b], w_dtype, i);
+        x[t * W + i] = fmaf(scale, sum, x[t * W + i]);
+    }
+}
+
+extern "C" int pe_normed_sum_add(float* x, const void* y0, const void* y1, const void* y2, const void* y3, int y_dtype,
+                                 const void* w0, const void* w1, const void* w2, const void* w3, int w_dtype, int n, int T, int W,
+                                 float eps, float scale, void* stream) {
+    if (T <= 0) return 0;
+    if (n < 1 || n > 4) return PE_ERR_UNSUPPORTED;
+    NormedSumArgs a = {{y0, y1, y2, y3}, {w0, w1, w2, w3}, n};
+    cudaStream_t s = (cudaStream_t)stream;
+    if (y_dtype == PE_F32) PE_TRY(pe_launch(normed_sum_add_kernel<float>, T, 256, 0, s, x, a, w_dtype, W, eps, scale));
+    else if (y_dtype == PE_BF16) PE_TRY(pe_launch(normed_sum_add_kernel<bf16>, T, 256, 0, s, x, a, w_dtype, W, eps, scale));
+    else return PE_ERR_UNSUPPORTED;
+    PE_LAUNCH_CHECK();
+    return 0;
+}
+
+// ---------------------------------------------------------------- x += scale * y
+template <typename T>
+__global__ void scaled_add_kernel(float* x, const T* y, float scale, size_t total) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
+        x[i] = fmaf(scale, to_f(y[i]), x[i]);
+}
+
+extern "C" int pe_scaled_add(float* x, const void* y, int dtype, float scale, long long total, void* stream) {
+    if (total <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    if (dtype == PE_F32) PE_TRY(pe_launch(scaled_add_kernel<float>, blocks, 256, 0, s, x, (const float*)y, scale, (size_t)total));
+    else if (dtype == PE_BF16) PE_TRY(pe_launch(scaled_add_kernel<bf16>, blocks, 256, 0, s, x, (const bf16*)y, scale, (size_t)total));
+    else return PE_ERR_UNSUPPORTED;
+    PE_LAUNCH_CHECK();
+    return 0;
+}
+
+// ---------------------------------------------------------------- x[t, :] += rows[t, :] + vec[:]
+// rows [T, W] float32 or null, vec [W] in either dtype or null.
+__global__ void add_rows_kernel(float* x, const float* rows, const void* vec, int v_dtype, int W, size_t total) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        float f = x[i];
+        if (rows) f += rows[i];
+        if (vec) f += load_as_f(vec, v_dtype, i % W);
+        x[i] = f;
+    }
+}
+
+extern "C" int pe_add_rows(float* x, const float* rows, const void* vec, int v_dtype, int T, int W, void* stream) {
+    if (T <= 0) return 0;
+    const size_t total = (size_t)T * W;
+    const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    PE_TRY(pe_launch(add_rows_kernel, blocks, 256, 0, (cudaStream_t)stream, x, rows, vec, v_dtype, W, total));
+    PE_LAUNCH_CHECK();
+    return 0;
+}
+
+// ---------------------------------------------------------------- gated activation, a weight per group of columns
+// gu [T, 2I] = gate | up; out[t, c] = act(gate[t, c]) * up[t, c] * colw[t, g(c)], with g(c) = min(c / group, n_groups - 1)
+// (colw [T, n_groups] float32 or null: no weights).  The product is formed in float32.
+template <typename T>
+__global__ void gated_act_kernel(const T* gu, T* out, int I, int act, const float* colw, int group, int n_groups, size_t total) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = idx / I, c = idx % I;
+        float f = go_act(to_f(gu[t * 2 * I + c]), act) * to_f(gu[t * 2 * I + I + c]);
+        if (colw) {
+            const int g = min((int)(c / group), n_groups - 1);
+            const float w = colw[t * n_groups + g];
+            f = w == 0.f ? 0.f : f * w;
+        }
+        out[idx] = from_f<T>(f);
+    }
+}
+
+extern "C" int pe_gated_act(const void* gu, void* out, int dtype, int T, int I, int act, const float* colw, int group, int n_groups,
+                            void* stream) {
+    if (T <= 0 || I <= 0) return 0;
+    if (colw && (group <= 0 || n_groups <= 0)) return PE_ERR_UNSUPPORTED;
+    const size_t total = (size_t)T * I;
+    const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == PE_F32) PE_TRY(pe_launch(gated_act_kernel<float>, blocks, 256, 0, s, (const float*)gu, (float*)out, I, act, colw, group, n_groups, total));
+    else if (dtype == PE_BF16) PE_TRY(pe_launch(gated_act_kernel<bf16>, blocks, 256, 0, s, (const bf16*)gu, (bf16*)out, I, act, colw, group, n_groups, total));
+    else return PE_ERR_UNSUPPORTED;
+    PE_LAUNCH_CHECK();
+    return 0;
+}
+
+// ---------------------------------------------------------------- the choice of experts
+// logits [T, ld] float32: columns 0 .. E-1 are the router's, column E (extra != 0) the logit of a gate for a part that
+// every token uses.  weights [T, E + extra] float32: the softmax over the `top` largest logits at their places, zero at
+// the others (of equal logits the lower index is taken first); the extra column holds sigmoid(logit).  ids [T, top] int32
+// (or null) receives the chosen experts, largest logit first.  A warp a token.
+__global__ void __launch_bounds__(128) moe_route_kernel(const float* logits, int ld, int E, int top, int extra, float* weights,
+                                                        int* ids, int T) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (t >= T) return;
+    const float* z = logits + (size_t)t * ld;
+    float* w = weights + (size_t)t * (E + extra);
+    for (int e = lane; e < E; e += 32) w[e] = 0.f;
+    if (extra && lane == 0) w[E] = go_sigmoid(z[E]);
+    __syncwarp();
+    float zmax = 0.f, sum = 0.f;
+    unsigned long long taken_lo = 0ull;                 // the lane's taken places (a lane sees E / 32 <= 64 of them)
+    for (int k = 0; k < top; ++k) {
+        float best = -INFINITY;
+        int at = 0x7fffffff;
+        for (int e = lane, i = 0; e < E; e += 32, ++i) {
+            if (taken_lo >> i & 1ull) continue;
+            const float v = z[e];
+            if (v > best || (v == best && e < at)) { best = v; at = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+            if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+        }
+        if (at == 0x7fffffff) break;
+        if ((at & 31) == lane) taken_lo |= 1ull << (at >> 5);
+        if (k == 0) zmax = best;
+        const float p = expf(best - zmax);
+        sum += p;
+        if (lane == 0) { w[at] = p; if (ids) ids[(size_t)t * top + k] = at; }
+    }
+    __syncwarp();
+    const float inv = 1.0f / sum;
+    for (int e = lane; e < E; e += 32) w[e] *= inv;
+}
+
+extern "C" int pe_moe_route(const float* logits, int ld, int E, int top, int extra, float* weights, int* ids, int T, void* stream) {
+    if (T <= 0) return 0;
+    if (E <= 0 || E > 2048 || top <= 0 || top > E) return PE_ERR_UNSUPPORTED;
+    PE_TRY(pe_launch(moe_route_kernel, (T + 3) / 4, 128, 0, (cudaStream_t)stream, logits, ld, E, top, extra, weights, ids, T));
+    PE_LAUNCH_CHECK();
+    return 0;
+}

@@ -9,7 +9,7 @@ from typing import Optional
 
 import torch
 
-from .library import DTYPE_CODE, KernelError, check, core, extras, mixers, stream_ptr
+from .library import DTYPE_CODE, KernelError, check, core, extras, gated, mixers, stream_ptr
 
 PAGE = 64     # tokens per cache page; PE_PAGE in csrc/common.cuh
 
@@ -890,4 +890,154 @@ def attention_headmix(q: torch.Tensor, q_stride: int, n_heads: int, n_kv: int, h
                                    _ptr(sink), 0 if sink is None else _code(sink, "sink"), _ptr(mix),
                                    0 if mix is None else _code(mix, "mix"), qt, splits, ws.data_ptr(), stream_ptr()),
           "attention_headmix", 2 + (splits > 1))
+    return out
+
+
+# ---------------------------------------------------------------------------- gated mixers and routed feed-forwards
+
+LA_ACTIVATIONS = {"none": 0, "silu": 1}
+GATE_ACTIVATIONS = {"none": 0, "sigmoid": 1, "silu": 2, "gelu_tanh": 3}
+
+
+def linear_attention(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, n_heads: int, head_dim: int, v_head_dim: int,
+                     state: torch.Tensor, state_offset: int, row_first: torch.Tensor, row_lens: torch.Tensor, slots: torch.Tensor,
+                     chunked: bool, head_decay: Optional[torch.Tensor] = None, decay_logits: Optional[torch.Tensor] = None,
+                     inv_tau: float = 1.0, q_scale: float = 1.0, qk_activation: str = "none",
+                     v_activation: str = "none") -> torch.Tensor:
+    """o [T, H * Dv] float32 of S_t = diag(a_t) S_(t-1) + k_t v_t^T, o_t = S_t^T q_t per head, for q, k, v at columns
+    ``q_off``, ``k_off``, ``v_off`` of proj [T, ld] (packed sequences).  The decay is ``head_decay`` [H] float32 (one constant
+    a head) or sigmoid(``decay_logits`` [T, H * D])^``inv_tau`` (a number per key channel and token).  S [H, D, Dv] comes from
+    and returns to the sequences' float32 state at ``state_offset``.  ``chunked``: prompts, three launches over chunks of
+    the sequences; else token after token in one launch."""
+    T, ld = proj.shape
+    H, D, Dv = n_heads, head_dim, v_head_dim
+    _need(proj, "proj")
+    if max(q_off + H * D, k_off + H * D, v_off + H * Dv) > ld:
+        raise KernelError("q, k and v do not fit the rows of proj")
+    if (head_decay is None) == (decay_logits is None):
+        raise KernelError("linear attention takes either a decay per head or decay logits per channel")
+    if head_decay is not None:
+        _need(head_decay, "head_decay", torch.float32, (H,))
+    else:
+        _need(decay_logits, "decay_logits", None, (T, H * D))
+    sp, stride = _state_args(state, state_offset, H * D * Dv)
+    B = slots.shape[0]
+    out = torch.empty(T, H * Dv, dtype=torch.float32, device=proj.device)
+    lib = gated()
+    ws = None
+    if chunked:
+        from .workspace import scratch
+        ws = scratch("linear_attention", 4 * lib.pe_linear_attention_scratch_floats(T, B, H, D, Dv), proj.device).data_ptr()
+    check(lib.pe_linear_attention(proj.data_ptr(), _code(proj, "proj"), ld, q_off, k_off, v_off, _ptr(decay_logits),
+                                  0 if decay_logits is None else _code(decay_logits, "decay_logits"), H * D, _ptr(head_decay),
+                                  float(inv_tau), float(q_scale), LA_ACTIVATIONS[qk_activation], LA_ACTIVATIONS[v_activation],
+                                  sp, stride, row_first.data_ptr(), row_lens.data_ptr(), slots.data_ptr(), out.data_ptr(),
+                                  T, B, H, D, Dv, 1 if chunked else 0, ws, stream_ptr()), "linear_attention", 3 if chunked else 1)
+    return out
+
+
+def rotary_norm_store(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, v_head_dim: int, freq: Optional[torch.Tensor],
+                      rot_dims: int, unit_norm: bool, eps: float, tok_pos: torch.Tensor, tok_row: torch.Tensor,
+                      k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor], block_table: Optional[torch.Tensor],
+                      table_stride: int) -> None:
+    """In every query and key head of qkv [T, ld] (a row begins with H*D query, G*D key and G*Dv value entries), in place: entries (2i, 2i+1) below ``rot_dims`` are turned by
+    pos * freq[i] (``freq`` float32 [rot_dims / 2]; rot_dims 0: no rotation), then (``unit_norm``) the head is divided by its
+    root mean square; keys and values then go to their cache pages (skipped when ``k_pool`` is None)."""
+    T, ld = qkv.shape
+    _need(qkv, "qkv")
+    if ld < n_heads * head_dim + n_kv * head_dim + n_kv * v_head_dim:
+        raise KernelError("queries, keys and values do not fit the rows of qkv")
+    if rot_dims:
+        _need(freq, "freq", torch.float32, (rot_dims // 2,))
+    store = k_pool is not None
+    if store:
+        _need(k_pool, "k_pool", qkv.dtype); _need(v_pool, "v_pool", qkv.dtype); _need(block_table, "block_table", torch.int32)
+        if tuple(k_pool.shape[1:]) != (n_kv, PAGE, head_dim) or tuple(v_pool.shape[1:]) != (n_kv, PAGE, v_head_dim):
+            raise KernelError(f"cache pools must be [pages, {n_kv}, {PAGE}, {head_dim}] and [pages, {n_kv}, {PAGE}, {v_head_dim}], "
+                              f"not {tuple(k_pool.shape)} and {tuple(v_pool.shape)}")
+    check(gated().pe_rotary_norm_store(qkv.data_ptr(), _code(qkv, "qkv"), ld, T, n_heads, n_kv, head_dim, v_head_dim, _ptr(freq),
+                                       rot_dims, 1 if unit_norm else 0, float(eps), tok_pos.data_ptr(), tok_row.data_ptr(),
+                                       _ptr(k_pool), _ptr(v_pool), _ptr(block_table), table_stride, 1 if store else 0,
+                                       stream_ptr()), "rotary_norm_store")
+
+
+def gated_norm(o: torch.Tensor, group: int, weight: Optional[torch.Tensor], eps: float, gate: Optional[torch.Tensor], gate_offset: int,
+               gate_activation: str, out_dtype: torch.dtype) -> torch.Tensor:
+    """Rows o [T, C] (float32 or ``out_dtype``): every run of ``group`` channels divided by its root mean square and multiplied
+    by ``weight`` [group] (group 0: no norm), then by act(gate[t, gate_offset + c]) of gate [T, ld] (None: no gate)."""
+    T, C = o.shape
+    _need(o, "o")
+    if weight is not None:
+        _need(weight, "weight", None, (group,))
+    if gate is not None:
+        _need(gate, "gate", out_dtype)
+        if gate_offset + C > gate.shape[1]:
+            raise KernelError("the gate's columns do not fit its rows")
+    out = torch.empty(T, C, dtype=out_dtype, device=o.device)
+    check(gated().pe_gated_norm(o.data_ptr(), _code(o, "o"), T, C, group, _ptr(weight), 0 if weight is None else _code(weight, "weight"),
+                                float(eps), _ptr(gate), 0 if gate is None else gate.shape[1], gate_offset,
+                                GATE_ACTIVATIONS[gate_activation], out.data_ptr(), _code(out, "out"), stream_ptr()), "gated_norm")
+    return out
+
+
+def normed_sum_add(x: torch.Tensor, branches, weights, eps: float, scale: float) -> torch.Tensor:
+    """x += scale * sum_i rmsnorm(branches[i]) * weights[i] on the float32 stream [T, W]; up to four branches of one dtype."""
+    T, W = x.shape
+    _need(x, "x", torch.float32)
+    n = len(branches)
+    for y, w in zip(branches, weights):
+        _need(y, "branch", branches[0].dtype, (T, W)); _need(w, "weight", weights[0].dtype, (W,))
+    ys = [y.data_ptr() for y in branches] + [None] * (4 - n)
+    ws = [w.data_ptr() for w in weights] + [None] * (4 - n)
+    check(gated().pe_normed_sum_add(x.data_ptr(), *ys, _code(branches[0], "branch"), *ws, _code(weights[0], "weight"), n, T, W,
+                                    float(eps), float(scale), stream_ptr()), "normed_sum_add")
+    return x
+
+
+def scaled_add(x: torch.Tensor, y: torch.Tensor, scale: float) -> torch.Tensor:
+    """x += scale * y on the float32 stream; y in either dtype."""
+    _need(x, "x", torch.float32); _need(y, "y", None, x.shape)
+    check(gated().pe_scaled_add(x.data_ptr(), y.data_ptr(), _code(y, "y"), float(scale), x.numel(), stream_ptr()), "scaled_add")
+    return x
+
+
+def add_rows(x: torch.Tensor, rows: Optional[torch.Tensor], vec: Optional[torch.Tensor]) -> torch.Tensor:
+    """x[t] += rows[t] + vec on the float32 stream [T, W]; ``rows`` float32 [T, W] or None, ``vec`` [W] in either dtype or None."""
+    T, W = x.shape
+    _need(x, "x", torch.float32)
+    if rows is not None:
+        _need(rows, "rows", torch.float32, (T, W))
+    if vec is not None:
+        _need(vec, "vec", None, (W,))
+    check(gated().pe_add_rows(x.data_ptr(), _ptr(rows), _ptr(vec), 0 if vec is None else _code(vec, "vec"), T, W, stream_ptr()), "add_rows")
+    return x
+
+
+def gated_act(gate_up: torch.Tensor, activation: str, col_weights: Optional[torch.Tensor] = None, group: int = 0) -> torch.Tensor:
+    """act(gate) * up [T, I] for gate_up [T, 2I] = gate | up.  ``col_weights`` float32 [T, n]: column c is also multiplied by
+    col_weights[t, min(c // group, n - 1)] (a zero weight gives an exact zero)."""
+    T, I2 = gate_up.shape
+    _need(gate_up, "gate_up")
+    n = 0
+    if col_weights is not None:
+        n = col_weights.shape[1]
+        _need(col_weights, "col_weights", torch.float32, (T, n))
+    out = torch.empty(T, I2 // 2, dtype=gate_up.dtype, device=gate_up.device)
+    check(gated().pe_gated_act(gate_up.data_ptr(), out.data_ptr(), _code(gate_up, "gate_up"), T, I2 // 2, GATE_ACTIVATIONS[activation],
+                               _ptr(col_weights), group, n, stream_ptr()), "gated_act")
+    return out
+
+
+def moe_route(logits: torch.Tensor, n_experts: int, top_k: int, extra: bool, ids: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Dense routing weights float32 [T, E (+ 1)] from router logits float32 [T, E (+ 1)]: the softmax over each token's ``top_k``
+    largest logits at their places, zero elsewhere; with ``extra`` the last column is sigmoid(its logit).  ``ids`` int32
+    [T, top_k] receives the chosen experts."""
+    T = logits.shape[0]
+    cols = n_experts + (1 if extra else 0)
+    _need(logits, "logits", torch.float32, (T, cols))
+    if ids is not None:
+        _need(ids, "ids", torch.int32, (T, top_k))
+    out = torch.empty(T, cols, dtype=torch.float32, device=logits.device)
+    check(gated().pe_moe_route(logits.data_ptr(), cols, n_experts, top_k, 1 if extra else 0, out.data_ptr(), _ptr(ids), T,
+                               stream_ptr()), "moe_route")
     return out

@@ -21,6 +21,9 @@ EXTRA_SOURCES = ("linear_mma.cu", "linear_batch.cu", "gemm_splitk.cu")
 # whose weights are mixed across heads, the gated recurrence): compiled when a model with such a part is built.
 MIXER_SOURCES = ("layernorm_conv.cu", "attention_headmix.cu", "attention_headmix_mma.cu", "attention_headmix_flash.cu",
                  "gated_recurrence.cu")
+# The kernels of gated mixers and routed feed-forwards (the linear-attention recurrence, rotation of pairs with unit norm and
+# cache write, norms over groups of channels with a gate, sums of normed branches, gated activations, the choice of experts).
+GATED_SOURCES = ("linear_attention.cu", "gated_ops.cu")
 HEAD_DIM_SOURCES = ("attention_decode.cu", "attention_prefill.cu", "attention_prefill_tcgen05.cu")      # compiled per head size
 
 _SIGNATURES = {
@@ -56,6 +59,17 @@ _MIXER_SIGNATURES = {
     "pe_qknorm_store": [P, I, I, I, I, I, I, P, I, P, I, F, P, P, P, P, P, I, I, P],
     "pe_attention_flashmix": [P, I, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, P, P, I, P, P],
     "pe_attention_headmix_mma": [P, I, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, F, P, P, I, P, P],
+}
+
+_GATED_SIGNATURES = {
+    "pe_linear_attention": [P, I, I, I, I, I, P, I, I, P, F, F, I, I, P, LL, P, P, P, P, I, I, I, I, I, I, P, P],
+    "pe_rotary_norm_store": [P, I, I, I, I, I, I, I, P, I, I, F, P, P, P, P, P, I, I, P],
+    "pe_gated_norm": [P, I, I, I, I, P, I, F, P, I, I, I, P, I, P],
+    "pe_normed_sum_add": [P, P, P, P, P, I, P, P, P, P, I, I, I, I, F, F, P],
+    "pe_scaled_add": [P, P, I, F, LL, P],
+    "pe_add_rows": [P, P, P, I, I, I, P],
+    "pe_gated_act": [P, P, I, I, I, I, P, I, I, P],
+    "pe_moe_route": [P, I, I, I, I, P, P, I, P],
 }
 
 _EXTRA_SIGNATURES = {
@@ -137,6 +151,22 @@ def mixers() -> ctypes.CDLL:
         lib.pe_attention_headmix_mma_scratch_floats.restype = c_longlong
         _mixers = lib
     return _mixers
+
+
+_gated = None
+
+
+def gated() -> ctypes.CDLL:
+    """The library of the kernels of gated mixers and routed feed-forwards; compiled at the first call."""
+    global _gated
+    if _gated is None:
+        lib = build.load("gated", GATED_SOURCES)
+        declare(lib, _GATED_SIGNATURES)
+        lib.pe_set_pdl(0 if os.environ.get("PICO_ENGINE_PDL", "1") == "0" else 1)
+        lib.pe_linear_attention_scratch_floats.argtypes = [I, I, I, I, I]
+        lib.pe_linear_attention_scratch_floats.restype = c_longlong
+        _gated = lib
+    return _gated
 
 
 _extras = None

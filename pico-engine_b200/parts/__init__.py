@@ -9,7 +9,11 @@ from .input_conv import CausalConvAdd
 from .attention import GQAAttention
 from .attention_headmix import HeadMixAttention
 from .mingru import MinGRU
-from .feed_forward import DenseMLP, SwiGLU
+from .feed_forward import DenseMLP, GatedMLP, SwiGLU
+from .linear_attention import LinearAttention
+from .attention_gated import GatedAttention
+from .branch_sum import BranchSum
+from .mixture import Mixture
 from .block import Layer, parallel, pre_norm
 from .model import DecoderModel
 
@@ -17,4 +21,4 @@ __all__ = ["ARRANGEMENTS", "FEED_FORWARDS", "MIXERS", "NORMS", "POSITIONS", "Fee
            "Part", "Position", "StepContext", "build_part", "register_arrangement", "register_feed_forward",
            "register_mixer", "register_norm", "register_position", "RMSNorm", "NoPosition", "RotaryHalf",
            "GQAAttention", "SwiGLU", "Layer", "pre_norm", "DecoderModel", "LayerNorm", "SinusoidAdd", "CausalConvAdd",
-           "HeadMixAttention", "MinGRU", "DenseMLP", "parallel"]
+           "HeadMixAttention", "MinGRU", "DenseMLP", "parallel", "GatedMLP", "LinearAttention", "GatedAttention", "BranchSum", "Mixture"]

@@ -1,0 +1,104 @@
+"""Grouped softmax attention with an output gate, optional unit norm of queries and keys, and its position encoding."""
+from __future__ import annotations
+
+import torch
+
+from ..cache import CacheNeeds, KVNeed
+from ..config.specs import ConfigError, GatedAttentionSpec, NoPositionSpec, RotaryPairsSpec
+from ..ops import kernels, linear
+from ..weights.loader import ParamSpec
+from .base import Mixer, register_mixer
+
+
+def pair_frequencies(spec: RotaryPairsSpec, device) -> torch.Tensor:
+    """base^(-2i/dims) / factor for i < dims / 2, worked out in float64 and rounded once to float32."""
+    i = torch.arange(spec.dims // 2, dtype=torch.float64)
+    return (spec.base ** (-2.0 * i / spec.dims) / spec.factor).to(torch.float32).to(device)
+
+
+@register_mixer(GatedAttentionSpec)
+class GatedAttention(Mixer):
+    """One product for q, k, v and the gate; rotation of neighbouring pairs of q and k, unit norm of every head and the
+    cache write in one kernel (csrc/gated_ops.cu); attention over the cache (the kernels of grouped attention where keys
+    and values have one size that they take, else the float32-score kernels that take any two sizes); the heads times
+    sigmoid(gate); the output projection.  Angles, norms, scores, softmax and the gate are float32 in either dtype."""
+
+    takes_out_dtype = True      # apply(..., out_dtype=) gives the product's float32 sums where the caller goes on in float32
+
+    def __init__(self, spec: GatedAttentionSpec, dtype, device):
+        super().__init__(spec, dtype, device)
+        if spec.n_heads % spec.n_kv_heads:
+            raise ConfigError(f"{spec.n_heads} query heads cannot share {spec.n_kv_heads} key/value heads evenly")
+        if not isinstance(spec.position, (NoPositionSpec, RotaryPairsSpec)):
+            raise ConfigError("gated attention takes rotation of pairs or no position encoding")
+        if spec.head_dim > 256 or spec.v_head_dim > 256:
+            raise ConfigError(f"head sizes {spec.head_dim}/{spec.v_head_dim} are not taken: up to 256 are")
+        if spec.window is not None and spec.window <= 0:
+            raise ConfigError(f"window {spec.window} must be positive")
+        self.state_offset = 0
+        self.w_in = self.w_o = self.freq = None
+        # the kernels of grouped attention take equal key and value sizes: any up to 256 in float32, multiples of 16 in bfloat16
+        self.plain_kernels = spec.v_head_dim == spec.head_dim and (dtype == torch.float32 or spec.head_dim % 16 == 0)
+
+    def _widths(self):
+        s = self.spec
+        return s.n_heads * s.head_dim, s.n_kv_heads * s.head_dim, s.n_kv_heads * s.v_head_dim, s.n_heads * s.v_head_dim
+
+    def expected_tensors(self):
+        s, p = self.spec, self.spec.prefix
+        q, k, v, o = self._widths()
+        out = {p + s.q_name: ParamSpec((q, s.hidden)), p + s.k_name: ParamSpec((k, s.hidden)), p + s.v_name: ParamSpec((v, s.hidden)),
+               p + s.o_name: ParamSpec((s.hidden, o))}
+        if s.gate is not None:
+            out[p + s.gate] = ParamSpec((o, s.hidden))
+        return out
+
+    def take_tensors(self, get):
+        s, p = self.spec, self.spec.prefix
+        parts = [get(p + n) for n in (s.q_name, s.k_name, s.v_name)] + ([get(p + s.gate)] if s.gate is not None else [])
+        rows = sum(t.shape[0] for t in parts)
+        if rows % 8:                                       # rows of the product stay aligned for the attention kernels' vector loads
+            parts.append(torch.zeros(8 - rows % 8, s.hidden, dtype=parts[0].dtype, device=parts[0].device))
+        self.w_in = torch.cat(parts, dim=0).contiguous()
+        self.w_o = get(p + s.o_name)
+
+    def prepare(self, max_positions):
+        from ..ops.library import for_head_dim, gated, mixers
+        gated()                                            # build or load this part's kernels now, loudly
+        if not self.plain_kernels:
+            mixers()
+        elif self.dtype == torch.bfloat16:
+            for_head_dim(self.spec.head_dim)
+        if isinstance(self.spec.position, RotaryPairsSpec):
+            self.freq = pair_frequencies(self.spec.position, self.device)
+
+    def weights(self):
+        return [self.w_in, self.w_o]
+
+    def cache_needs(self):
+        s = self.spec
+        return CacheNeeds(kv=KVNeed(s.n_kv_heads, s.head_dim, s.window,
+                                    v_head_dim=None if s.v_head_dim == s.head_dim else s.v_head_dim))
+
+    def gated_heads(self, h, ctx, cache_entry, owns_cache):
+        """The heads' outputs times the gate [T, n_heads * v_head_dim] for normed rows h."""
+        s = self.spec
+        q_w, k_w, v_w, o_w = self._widths()
+        kv = ctx.kv(cache_entry)
+        proj = linear(h, self.w_in, out_dtype=ctx.dtype)
+        rot_dims = s.position.dims if isinstance(s.position, RotaryPairsSpec) else 0
+        kernels.rotary_norm_store(proj, s.n_heads, s.n_kv_heads, s.head_dim, s.v_head_dim, self.freq, rot_dims, s.qk_unit_norm,
+                                  s.norm_eps, ctx.tok_pos, ctx.tok_row, kv.k if owns_cache else None, kv.v if owns_cache else None,
+                                  kv.table if owns_cache else None, kv.stride)
+        if self.plain_kernels:
+            a = kernels.attention(proj, proj.shape[1], s.n_heads, s.n_kv_heads, s.head_dim, kv.k, kv.v, kv.table, kv.stride,
+                                  ctx.tok_pos, ctx.tok_row, s.window, s.scale, ctx, own_rows_only=owns_cache)
+        else:
+            a = kernels.attention_headmix(proj, proj.shape[1], s.n_heads, s.n_kv_heads, s.head_dim, s.v_head_dim, kv.k, kv.v,
+                                          kv.table, kv.stride, ctx.tok_pos, ctx.tok_row, s.window, s.scale, None, None, ctx)
+        if s.gate is None:
+            return a
+        return kernels.gated_norm(a, 0, None, s.norm_eps, proj, q_w + k_w + v_w, "sigmoid", ctx.dtype)
+
+    def apply(self, h, ctx, entry, cache_entry, owns_cache, out_dtype=None):
+        return linear(self.gated_heads(h, ctx, cache_entry, owns_cache), self.w_o, out_dtype=out_dtype or ctx.dtype)

@@ -66,7 +66,24 @@ class Layer:
 
 @register_arrangement("pre_norm")
 def pre_norm(layer: Layer, x, ctx, entry, cache_entry, owns_cache) -> None:
-    """x += mixer(norm(x)); x += feed_forward(norm(x))  (pico-engine src/pico_engine/model.py:167-237)."""
+    """x += mixer(norm(x)); x += feed_forward(norm(x))  (pico-engine src/pico_engine/model.py:167-237).  With a
+    ``residual_scale`` m other than 1 both sums are x += m * sublayer(norm(x)), formed in float32 from the sublayer's
+    output (a part may do the sum itself: ``add_scaled_to``)."""
+    m = layer.spec.residual_scale
+    if m != 1.0:
+        from ..ops import kernels
+        ctx.settle(x)
+        if layer.mixer is not None:
+            h = layer.mixer_norm.forward(x, ctx.dtype)
+            if hasattr(layer.mixer, "add_scaled_to"):
+                layer.mixer.add_scaled_to(x, h, m, ctx, entry, cache_entry, owns_cache)
+            else:
+                wide = {"out_dtype": x.dtype} if getattr(layer.mixer, "takes_out_dtype", False) else {}
+                kernels.scaled_add(x, layer.mixer.apply(h, ctx, entry, cache_entry, owns_cache, **wide).contiguous(), m)
+        if layer.feed_forward is not None:
+            wide = {"out_dtype": x.dtype} if getattr(layer.feed_forward, "takes_out_dtype", False) else {}
+            kernels.scaled_add(x, layer.feed_forward.apply(layer.feed_forward_norm.forward(x, ctx.dtype), ctx, **wide).contiguous(), m)
+        return
     if layer.mixer is not None:
         if not layer.mixer.takes_pending:
             ctx.settle(x)

@@ -3,7 +3,7 @@ from __future__ import annotations
 
 import torch
 
-from ..config.specs import ConfigError, DenseMLPSpec, SwiGLUSpec
+from ..config.specs import ConfigError, DenseMLPSpec, GatedMLPSpec, SwiGLUSpec
 from ..ops import kernels, linear
 from ..weights.loader import ParamSpec
 from .base import FeedForward, register_feed_forward
@@ -81,3 +81,39 @@ class DenseMLP(FeedForward):
     def add_output_to(self, x, h, ctx) -> None:
         """x += feed_forward(h) for rows h that are normed (and filtered) already."""
         linear(self._activation(h, ctx), self.w_down, accumulate_into=x)
+
+
+@register_feed_forward(GatedMLPSpec)
+class GatedMLP(FeedForward):
+    """down(act(gate(h)) * up(h)) without biases, gate and up as one product on concatenated weights; act is gelu
+    (tanh formula) or silu, and act(gate) * up is formed in float32."""
+
+    takes_out_dtype = True      # apply(..., out_dtype=) gives the product's float32 sums where the caller goes on in float32
+
+    def __init__(self, spec: GatedMLPSpec, dtype, device):
+        super().__init__(spec, dtype, device)
+        if spec.activation not in ("gelu_tanh", "silu"):
+            raise ConfigError(f"activation {spec.activation!r} is not known; known: gelu_tanh, silu")
+        self.w_gate_up = self.w_down = None
+
+    def expected_tensors(self):
+        s = self.spec
+        return {s.prefix + s.gate_name: ParamSpec((s.intermediate, s.hidden)), s.prefix + s.up_name: ParamSpec((s.intermediate, s.hidden)),
+                s.prefix + s.down_name: ParamSpec((s.hidden, s.intermediate))}
+
+    def take_tensors(self, get):
+        s = self.spec
+        self.w_gate_up = torch.cat([get(s.prefix + s.gate_name), get(s.prefix + s.up_name)], dim=0).contiguous()
+        self.w_down = get(s.prefix + s.down_name)
+
+    def prepare(self, max_positions):
+        from ..ops.library import gated
+        gated()                                            # build or load this part's kernels now, loudly
+
+    def apply(self, h, ctx, out_dtype=None):
+        if self.spec.activation == "silu":
+            from ..ops.linear import gate_up_swiglu
+            act = gate_up_swiglu(h, self.w_gate_up)
+        else:
+            act = kernels.gated_act(linear(h, self.w_gate_up, out_dtype=ctx.dtype), self.spec.activation)
+        return linear(act, self.w_down, out_dtype=out_dtype or ctx.dtype)

@@ -1,0 +1,76 @@
+"""A mixture of gated feed-forward experts with a router and an optional shared expert."""
+from __future__ import annotations
+
+import torch
+
+from ..config.specs import ConfigError, MixtureSpec
+from ..ops import kernels, linear
+from ..weights.loader import ParamSpec
+from .base import FeedForward, register_feed_forward
+
+
+@register_feed_forward(MixtureSpec)
+class Mixture(FeedForward):
+    """Every token uses the ``top_k`` experts with the largest router logits, weighted by the softmax over those logits;
+    a shared expert runs for every token, times one sigmoid gate.  Router and shared gate are one float32 product (their
+    weights are kept in float32), the choice and the weights one kernel (csrc/gated_ops.cu: dense weights [T, experts + 1],
+    zero for experts a token does not use).
+
+    The experts run as two products on concatenated weights: gate and up of all experts (and the shared one) at once,
+    then act(gate) * up * weight(token, expert) in float32, then one down product whose inner dimension runs over all
+    experts' hidden units, so that the weighted sum over experts happens in the product's float32 accumulator.  Hidden
+    units of experts a token does not use are exact zeros.  Every expert's weights are read in every step and every
+    token multiplies with all of them: right for steps whose tokens touch most experts, n_experts / top_k times
+    the necessary arithmetic for long prompts."""
+
+    takes_out_dtype = True      # apply(..., out_dtype=) gives the product's float32 sums where the caller goes on in float32
+
+    def __init__(self, spec: MixtureSpec, dtype, device):
+        super().__init__(spec, dtype, device)
+        if not 1 <= spec.top_k <= spec.n_experts:
+            raise ConfigError(f"top_k = {spec.top_k} must lie in 1 .. n_experts = {spec.n_experts}")
+        if spec.activation not in kernels.GATE_ACTIVATIONS:
+            raise ConfigError(f"activation {spec.activation!r} is not known")
+        self.w_router = self.w_gate_up = self.w_down = None
+
+    def _experts(self):
+        s = self.spec
+        names = [(s.prefix + s.expert_name.format(e) + ".", s.intermediate) for e in range(s.n_experts)]
+        if s.shared_intermediate is not None:
+            names.append((s.prefix + s.shared_name + ".", s.shared_intermediate))
+        return names
+
+    def expected_tensors(self):
+        s = self.spec
+        out = {s.prefix + s.router_name: ParamSpec((s.n_experts, s.hidden))}
+        for p, ff in self._experts():
+            out.update({p + s.gate_name: ParamSpec((ff, s.hidden)), p + s.up_name: ParamSpec((ff, s.hidden)),
+                        p + s.down_name: ParamSpec((s.hidden, ff))})
+        if s.shared_intermediate is not None:
+            out[s.prefix + s.shared_gate_name] = ParamSpec((1, s.hidden))
+        return out
+
+    def take_tensors(self, get):
+        s = self.spec
+        router = [get(s.prefix + s.router_name)] + ([get(s.prefix + s.shared_gate_name)] if s.shared_intermediate is not None else [])
+        self.w_router = torch.cat(router, dim=0).float().contiguous()           # router logits are float32 products
+        experts = self._experts()
+        self.w_gate_up = torch.cat([get(p + s.gate_name) for p, _ in experts] + [get(p + s.up_name) for p, _ in experts], dim=0).contiguous()
+        self.w_down = torch.cat([get(p + s.down_name) for p, _ in experts], dim=1).contiguous()
+
+    def prepare(self, max_positions):
+        from ..ops.library import gated
+        gated()                                            # build or load this part's kernels now, loudly
+
+    def routing(self, h):
+        """Dense weights float32 [T, n_experts (+ 1)] of rows h."""
+        s = self.spec
+        logits = linear(h, self.w_router, out_dtype=torch.float32)
+        return kernels.moe_route(logits, s.n_experts, s.top_k, s.shared_intermediate is not None)
+
+    def apply(self, h, ctx, out_dtype=None):
+        s = self.spec
+        weights = self.routing(h)
+        gate_up = linear(h, self.w_gate_up, out_dtype=ctx.dtype)
+        act = kernels.gated_act(gate_up, s.activation, weights, s.intermediate)
+        return linear(act, self.w_down, out_dtype=out_dtype or ctx.dtype)

@@ -25,6 +25,8 @@ class DecoderModel:
         self.final_norm = build_part(NORMS, "norm", plan.final_norm, dtype, self.device)
         self.embedding_position = None if plan.embedding_position is None else \
             build_part(STREAM_POSITIONS, "stream position", plan.embedding_position, dtype, self.device)
+        self.stream_vectors: Dict[str, torch.Tensor] = {}      # [rows, hidden] tensors whose rows schedule entries add to the stream
+        self._keeps_embedding = any(e.add_embedding for e in plan.schedule)
         self.embedding: Optional[torch.Tensor] = None
         self.head: Optional[torch.Tensor] = None
 
@@ -43,6 +45,8 @@ class DecoderModel:
             out.update(part.expected_tensors())
         if p.head is not None:
             out[p.head] = ParamSpec((p.vocab_size, p.hidden_size))
+        for name, rows in p.stream_vectors:
+            out[name] = ParamSpec((rows, p.hidden_size))
         return out
 
     def take_tensors(self, get) -> None:
@@ -50,6 +54,7 @@ class DecoderModel:
         for part in self._parts():
             part.take_tensors(get)
         self.head = self.embedding if self.plan.head is None else get(self.plan.head)
+        self.stream_vectors = {name: get(name) for name, _ in self.plan.stream_vectors}
 
     def prepare(self, max_positions: int) -> None:
         for part in self._parts():
@@ -66,8 +71,13 @@ class DecoderModel:
         x = kernels.embed(self.embedding, token_ids)
         if self.embedding_position is not None:
             self.embedding_position.add_to(x, ctx)
+        x0 = x.clone() if self._keeps_embedding else None
         for e, entry in enumerate(self.plan.schedule):
             cache_entry = e if entry.cache_of is None else entry.cache_of
+            if entry.add_embedding or entry.add_vector is not None:
+                ctx.settle(x)
+                vec = None if entry.add_vector is None else self.stream_vectors[entry.add_vector[0]][entry.add_vector[1]]
+                kernels.add_rows(x, x0 if entry.add_embedding else None, vec)
             self.layers[entry.layer].run(x, ctx, e, cache_entry, entry.cache_of is None)
         ctx.settle(x)
         return x

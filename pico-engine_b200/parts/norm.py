@@ -10,7 +10,8 @@ from .base import Norm, register_norm
 @register_norm(RMSNormSpec)
 class RMSNorm(Norm):
     """y = x * rsqrt(mean(x^2) + eps) * w in float32 (pico-engine src/pico_engine/kernels.py:14-23).
-    The weight stays in the dtype it was stored in."""
+    The weight stays in the dtype it was stored in; with ``one_plus`` the stored vector v lies around zero, w = 1 + v is
+    formed once in float32 and kept so."""
 
     def __init__(self, spec: RMSNormSpec, dtype, device):
         super().__init__(spec, dtype, device)
@@ -18,10 +19,12 @@ class RMSNorm(Norm):
         self.eps = spec.eps
 
     def expected_tensors(self):
-        return {self.spec.weight: ParamSpec((self.spec.size,), init="one_plus_normal")}
+        return {self.spec.weight: ParamSpec((self.spec.size,), init="normal" if self.spec.one_plus else "one_plus_normal")}
 
     def take_tensors(self, get):
         self.weight = get(self.spec.weight)
+        if self.spec.one_plus:
+            self.weight = (1.0 + self.weight.float()).contiguous()
 
     def forward(self, x, out_dtype, rows_index=None):
         return kernels.rmsnorm(x, self.weight, self.eps, out_dtype, rows_index)
