@@ -157,12 +157,18 @@ def gated_mlp(h, w, p, act):
     return lin(w[p + "down"], act(lin(w[p + "gate"], h)) * lin(w[p + "up"], h))
 
 
+ROUTER_GAPS = None      # a list: every call of ``mixture`` appends, per token, how far the last chosen logit lies above the next one
+
+
 def mixture(h, w, p, mlp):
     """Every token takes its ``top`` experts with the largest router logits, weighted by the softmax over those
     logits alone; a shared expert, scaled by one sigmoid gate a token, is added."""
     n = h.shape[0]
     E, top = mlp["router"]["experts"], mlp["router"]["top"]
     z = lin(w[p + "router"], h)
+    if ROUTER_GAPS is not None and top < E:
+        ordered = z.sort(-1, descending=True).values
+        ROUTER_GAPS.append(ordered[:, top - 1] - ordered[:, top])
     out = torch.zeros(n, w[p + "e0.down"].shape[0], dtype=h.dtype)
     for t in range(n):
         order = sorted(range(E), key=lambda e: -float(z[t, e]))[:top]
