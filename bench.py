@@ -62,7 +62,7 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration has (recorded in config)")
-    ap.add_argument("--design", default=None, choices=["mebalorn"],
+    ap.add_argument("--design", default=None, choices=["mebalorn", "kevelorn"],
                     help="instead of the default workload: prefill and decode throughput of this design at a few layer sizes "
                          "beside the Qwen2 decoder at equal widths, and its kernels beside the like Qwen2 kernels")
     ap.add_argument("--sizes", default="s,m", help="with --design: which of the sizes s, m, l")
@@ -70,7 +70,7 @@ def main() -> int:
     if args.design:
         from pico_engine import design_compare
         pk, pk_kind = peaks()
-        rec = design_compare.compare([x for x in args.sizes.split(",") if x], 2048, 8, 2048, pk)
+        rec = design_compare.compare([x for x in args.sizes.split(",") if x], 2048, 8, 2048, pk, args.design)
         rec.update(design=args.design, beside="Qwen2ForCausalLM", dtype="bf16", data="synthetic", peaks=pk_kind)
         print(json.dumps(rec))
         return 0

@@ -108,8 +108,34 @@ def kv_bytes_per_token(engine) -> int:
 
 
 def decode_step_bytes(engine, batch: int, mean_context: float) -> float:
-    """What a decode step has to read: every weight it uses once, and the cache of the live sequences."""
-    return engine.model.step_weight_bytes() + batch * mean_context * kv_bytes_per_token(engine)
+    """What a decode step has to move: every weight it uses once, the keys and values the live sequences can see (a
+    windowed layer's window at most), and the sequences' fixed-size states, read and written."""
+    total = float(engine.model.step_weight_bytes())
+    itemsize = torch.empty(0, dtype=engine.dtype).element_size()
+    for need in engine.model.cache_needs():
+        if need is None:
+            continue
+        if need.kv is not None:
+            v_heads, v_dim = need.kv.value_shape
+            seen = mean_context if need.kv.window is None else min(mean_context, need.kv.window)
+            total += batch * seen * (need.kv.n_kv_heads * need.kv.head_dim + v_heads * v_dim) * itemsize
+        if need.state_elems:
+            total += 2.0 * batch * need.state_elems * (4 if need.state_dtype == "float32" else itemsize)
+    return total
+
+
+def _mixing_flops(spec, tokens: int) -> float:
+    """Multiply-adds times two of a mixer beyond its matrices: causal (windowed) attention, or the updates and reads of a
+    matrix state; a sum of branches is the sum of its branches."""
+    if hasattr(spec, "branches"):
+        return sum(_mixing_flops(b, tokens) for b in spec.branches)
+    if hasattr(spec, "n_kv_heads"):
+        w = spec.window
+        seen = sum(min(p + 1, w) if w else p + 1 for p in range(tokens))
+        return 2.0 * spec.n_heads * (spec.head_dim + getattr(spec, "v_head_dim", spec.head_dim)) * seen
+    if hasattr(spec, "n_heads") and hasattr(spec, "v_head_dim"):
+        return 4.0 * spec.n_heads * spec.head_dim * spec.v_head_dim * tokens
+    return 0.0
 
 
 def prefill_flops(engine, tokens: int) -> float:
@@ -122,11 +148,8 @@ def prefill_flops(engine, tokens: int) -> float:
         for part in (layer.mixer, layer.feed_forward):
             if part is not None:
                 flops += sum(2.0 * tokens * t.numel() for t in part.weights() if t.dim() == 2)
-        spec = layer.mixer.spec if layer.mixer is not None else None
-        if hasattr(spec, "n_heads"):
-            w = spec.window
-            seen = sum(min(p + 1, w) if w else p + 1 for p in range(tokens))
-            flops += 4.0 * spec.n_heads * spec.head_dim * seen
+        if layer.mixer is not None:
+            flops += _mixing_flops(layer.mixer.spec, tokens)
     return flops + 2.0 * model.head.numel()
 
 

@@ -48,6 +48,33 @@ SHAPES.update({
 })
 
 
+def kevelorn_shape(width: int, heads: int, kv_heads: int, dim: int, ff: int, layers: int, vocab: int, window: int = 1024,
+                   experts: int = 8, top: int = 2) -> dict:
+    """A Kevelorn config.json whose layers take these four forms in turn: fixed-decay linear attention + dense feed-forward,
+    learned-decay linear attention + mixture, windowed softmax attention beside linear attention + dense, fixed-decay linear
+    attention + mixture.  Experts and the shared expert are a quarter as wide as the dense feed-forward."""
+    decay = lambda n: [1.0 - 2.0 ** -(3 + h % 6) for h in range(n)]
+    dense = {"kind": "dense", "ff": ff}
+    moe = {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": ff // 4}, "shared": {"ff": ff // 4}}
+    lightning = {"heads": heads, "dim": dim, "vdim": dim, "decay": decay(heads)}
+    half = {"heads": max(heads // 2, 1), "dim": dim, "vdim": dim, "decay": decay(max(heads // 2, 1))}
+    left = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "mask": {"size": window},
+            "rot": {"base": 10000.0, "dims": dim, "scaling": {"factor": 4.0}}}
+    forms = [{"type": "lightning", "mixer": lightning, "mlp": dense},
+             {"type": "gla", "mixer": {"heads": heads, "dim": dim, "vdim": dim, "tau": 16.0}, "mlp": moe},
+             {"type": "parallel", "mixer": {"left": left, "right": half}, "mlp": dense},
+             {"type": "lightning", "mixer": lightning, "mlp": moe}]
+    return {"architecture": "Kevelorn", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "residual_mult": 0.5,
+            "layers": [dict(forms[i % 4]) for i in range(layers)]}
+
+
+SHAPES.update({
+    "kevelorn-tiny": kevelorn_shape(64, 4, 2, 16, 160, 4, 256, window=40, experts=4),
+    "kevelorn-0.5b": kevelorn_shape(896, 14, 2, 64, 4864, 24, 151936),          # the widths of qwen2.5-0.5b
+    "kevelorn-7b": kevelorn_shape(3584, 28, 4, 128, 18944, 28, 152064),         # the widths of qwen2.5-7b
+})
+
+
 def with_layers(d: dict, n: int) -> dict:
     """The shape with only its first ``n`` layers."""
     d = dict(d)

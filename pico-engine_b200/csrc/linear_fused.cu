@@ -54,6 +54,7 @@ struct LfArgs {
     const bf16* W;            // [N, K]
     const void* bias; int bias_dtype;
     void* out;                // STORE: [M, N]; ACCUM: float [M, N]; SWIGLU: bf16 [M, I]; ROPE: bf16 [M, n_q * hd]
+    float out_scale;          // ACCUM: out += out_scale * (a . W^T + bias)
     int M, N, K;
     int rows;                 // STORE/ACCUM: rows of W per CTA, 8 or 16
     int chunk, stages;        // columns per bulk copy (a multiple of 32) and copies in flight per row
@@ -444,7 +445,7 @@ __global__ void __launch_bounds__(32 * LF_WARPS, LF_MIN_CTAS(NT, RT, EPI)) linea
                 const size_t o = (size_t)m * p.N + n;
                 if (EPI == LF_STORE_F32) ((float*)p.out)[o] = v;
                 else if (EPI == LF_STORE_BF16) ((bf16*)p.out)[o] = __float2bfloat16_rn(v);
-                else atomicAdd((float*)p.out + o, v);     // the only sum into this element: a reduction in memory, no read to wait for
+                else atomicAdd((float*)p.out + o, p.out_scale * v);     // the only sum into this element: a reduction in memory, no read to wait for
             }
         }
     }
@@ -558,16 +559,17 @@ static bool lf_aligned(const void* p) { return (((uintptr_t)p) & 15) == 0; }
 
 // x += a . W^T (+ bias) or out = a . W^T (+ bias); `a` bfloat16 [M <= 16, K], or with `x_norm`
 // the float32 rows whose RMSNorm (weights norm_w, eps) is the operand.
-// epilogue: 0 store float32, 1 store bfloat16, 2 add into float32 out.
-extern "C" int pe_linear_fused(const void* a, const float* x_norm, const void* norm_w, int norm_w_dtype, float eps,
-                               const void* W, const void* bias, int bias_dtype, void* out, int epilogue, int M, int N,
-                               int K, int* status, void* stream) {
+// epilogue: 0 store float32, 1 store bfloat16, 2 add into float32 out, times out_scale.
+extern "C" int pe_linear_fused_scaled(const void* a, const float* x_norm, const void* norm_w, int norm_w_dtype, float eps,
+                                      const void* W, const void* bias, int bias_dtype, void* out, int epilogue, float out_scale,
+                                      int M, int N, int K, int* status, void* stream) {
     if (M <= 0 || N <= 0) return 0;
     if (M > 16 || K <= 0 || K % 8 || epilogue < 0 || epilogue > 2 || !lf_aligned(W) || !lf_aligned(x_norm ? (const void*)x_norm : a))
         return PE_ERR_UNSUPPORTED;
     LfArgs p = {};
     p.A = (const bf16*)a; p.X = x_norm; p.norm_w = norm_w; p.norm_w_dtype = norm_w_dtype; p.eps = eps;
     p.W = (const bf16*)W; p.bias = bias; p.bias_dtype = bias_dtype; p.out = out; p.M = M; p.N = N; p.K = K;
+    p.out_scale = out_scale;
     p.rows = (N + 15) / 16 >= 148 ? 16 : 8;                  // small matrices: more, thinner CTAs
     const int tiles = (N + p.rows - 1) / p.rows;
     cudaStream_t s = (cudaStream_t)stream;
@@ -579,6 +581,12 @@ extern "C" int pe_linear_fused(const void* a, const float* x_norm, const void* n
     if (epilogue == 0) return lf_launch<LF_PLAIN, LF_STORE_F32>(p, tiles, status, s);
     if (epilogue == 1) return lf_launch<LF_PLAIN, LF_STORE_BF16>(p, tiles, status, s);
     return lf_launch<LF_PLAIN, LF_ACCUM>(p, tiles, status, s);
+}
+
+extern "C" int pe_linear_fused(const void* a, const float* x_norm, const void* norm_w, int norm_w_dtype, float eps,
+                               const void* W, const void* bias, int bias_dtype, void* out, int epilogue, int M, int N,
+                               int K, int* status, void* stream) {
+    return pe_linear_fused_scaled(a, x_norm, norm_w, norm_w_dtype, eps, W, bias, bias_dtype, out, epilogue, 1.0f, M, N, K, status, stream);
 }
 
 // act[M, I] = silu(h . Wg^T) * (h . Wu^T), h = RMSNorm(x); W = [Wg; Wu] is [2I, K].

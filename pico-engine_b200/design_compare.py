@@ -1,10 +1,11 @@
 """Two designs side by side at equal layer widths: the Mebalorn decoder (layer norm + input convolution, attention
-with mixed heads or a minGRU recurrence, a dense relu^2 feed-forward, both halves in parallel) and the dense Qwen2
-decoder, this library's closest other model.  Random weights; prefill and decode throughput of a few layers, and
+with mixed heads or a minGRU recurrence, a dense relu^2 feed-forward, both halves in parallel) or the Kevelorn decoder
+(linear attention with fixed or learned decay, windowed softmax attention with an output gate beside it, gated dense
+feed-forwards and mixtures of experts) and the dense Qwen2 decoder, this library's closest other model.  Random weights; prefill and decode throughput of a few layers, and
 the kernels of the new design each beside the Qwen2 kernel that does the like job, as fractions of the measured
 copy bandwidth or matrix throughput.
 
-    python -m pico_engine.design_compare [--sizes s,m,l] [--tokens 2048] [--batch 8] [--context 2048] [--output FILE]
+    python -m pico_engine.design_compare [--design mebalorn|kevelorn] [--sizes s,m,l] [--tokens 2048] [--batch 8] [--context 2048] [--output FILE]
 """
 from __future__ import annotations
 
@@ -28,6 +29,15 @@ def mebalorn_config(size: str) -> dict:
     from .config.shapes import mebalorn_shape
     W, H, G, D, F, L = SIZES[size]
     return mebalorn_shape(W, H, G, D, F, L, VOCAB, taps=TAPS)
+
+
+def kevelorn_config(size: str) -> dict:
+    from .config.shapes import kevelorn_shape
+    W, H, G, D, F, L = SIZES[size]
+    return kevelorn_shape(W, H, G, D, F, L, VOCAB)
+
+
+DESIGNS = {"mebalorn": mebalorn_config, "kevelorn": kevelorn_config}
 
 
 def qwen2_config(size: str) -> dict:
@@ -102,7 +112,78 @@ def _decode_context(eng, batch: int, context: int):
     return slots, eng.stepper.context(lay, dev, [1] * batch, starts, slots)
 
 
-def kernel_times(size: str, tokens: int, batch: int, context: int, peaks: dict) -> Dict[str, dict]:
+def kevelorn_kernel_times(eng, size: str, tokens: int, batch: int, context: int, entry) -> None:
+    """The kernels that only the Kevelorn parts have, each at the sizes of this shape's layers."""
+    W, H, G, D, F, L = SIZES[size]
+    bf = torch.bfloat16
+    sched = eng.model.plan.schedule
+    kind = lambda e: type(eng.model.layers[sched[e].layer].mixer).__name__
+    e_fix = next(e for e in range(len(sched)) if kind(e) == "LinearAttention" and eng.model.layers[sched[e].layer].mixer.head_decay is not None)
+    e_gla = next(e for e in range(len(sched)) if kind(e) == "LinearAttention" and eng.model.layers[sched[e].layer].mixer.head_decay is None)
+    e_par = next(e for e in range(len(sched)) if kind(e) == "BranchSum")
+    fix = eng.model.layers[sched[e_fix].layer].mixer
+    left = eng.model.layers[sched[e_par].layer].mixer.branches[0]
+    moe = eng.model.layers[sched[e_gla].layer].feed_forward
+    state_bytes = H * D * D * 4
+
+    def recurrences(ctx, T, B, chunked, label):
+        proj = torch.randn(T, 4 * H * D, device="cuda").to(bf)
+        z = torch.randn(T, H * D, device="cuda")
+        work = 4.0 * H * D * D * T * (2 if chunked else 1)        # multiply-adds x 2, and the chunked way walks every chunk twice
+        moved = T * 4 * H * D * 2 + T * H * D * 4 + 2 * B * state_bytes
+        us = device_us(lambda: kernels.linear_attention(proj, 0, H * D, 2 * H * D, H, D, D, ctx.state(e_fix), 0, ctx.row_first, ctx.row_lens,
+                                                        ctx.slots, chunked, head_decay=fix.head_decay, qk_activation="silu", v_activation="silu"))
+        entry(f"{label} recurrence, fixed decay", us, nbytes=moved)
+        out[f"{label} recurrence, fixed decay"]["float32_tflops_per_s"] = work / us / 1e6
+        us = device_us(lambda: kernels.linear_attention(proj, 0, H * D, 2 * H * D, H, D, D, ctx.state(e_gla), 0, ctx.row_first, ctx.row_lens,
+                                                        ctx.slots, chunked, decay_logits=z, inv_tau=1 / 16.0, q_scale=D ** -0.5))
+        entry(f"{label} recurrence, learned decay", us, nbytes=moved + T * H * D * 4)
+        out[f"{label} recurrence, learned decay"]["float32_tflops_per_s"] = work / us / 1e6
+
+    out = entry.out
+    slot, ctx = _prompt_context(eng, tokens)
+    kv = ctx.kv(e_par)
+    recurrences(ctx, tokens, 1, True, "prefill")
+    qkvg = torch.randn(tokens, left.w_in.shape[0], device="cuda").to(bf)
+    entry("prefill pair rotation + unit norm + cache write", device_us(lambda: kernels.rotary_norm_store(
+        qkvg, H, G, D, D, left.freq, D, True, 1e-6, ctx.tok_pos, ctx.tok_row, kv.k, kv.v, kv.table, kv.stride)), nbytes=tokens * (H + 2 * G) * D * 2 * 2)
+    window = left.spec.window
+    seen = sum(min(p + 1, window) for p in range(tokens))
+    entry("prefill attention (window)", device_us(lambda: kernels.attention(
+        qkvg, qkvg.shape[1], H, G, D, kv.k, kv.v, kv.table, kv.stride, ctx.tok_pos, ctx.tok_row, window, D ** -0.5, ctx)), flops=4.0 * H * D * seen)
+    o = torch.randn(tokens, H * D, device="cuda")
+    entry("prefill norm over heads x gate", device_us(lambda: kernels.gated_norm(o, H * D, fix.norm, 1e-6, qkvg, 0, "sigmoid", bf)),
+          nbytes=tokens * H * D * (4 + 2 + 2))
+    entry("prefill norm per head x gate", device_us(lambda: kernels.gated_norm(o, D, fix.norm[:D].contiguous(), 1e-6, qkvg, 0, "silu", bf)),
+          nbytes=tokens * H * D * (4 + 2 + 2))
+    ob = o.to(bf)
+    entry("prefill heads x gate", device_us(lambda: kernels.gated_norm(ob, 0, None, 1e-6, qkvg, 0, "sigmoid", bf)), nbytes=tokens * H * D * 2 * 3)
+    x = torch.randn(tokens, W, device="cuda")
+    ys = [torch.randn(tokens, W, device="cuda") for _ in range(2)]
+    ws = eng.model.layers[sched[e_par].layer].mixer.out_norms
+    entry("prefill two normed branches into the stream", device_us(lambda: kernels.normed_sum_add(x, ys, ws, 1e-6, 0.25)), nbytes=tokens * W * 4 * 4)
+    entry("prefill scaled residual sum", device_us(lambda: kernels.scaled_add(x, ys[0], 0.5)), nbytes=tokens * W * 4 * 3)
+    gu = torch.randn(tokens, 2 * F, device="cuda").to(bf)
+    entry("prefill gelu(gate) x up", device_us(lambda: kernels.gated_act(gu, "gelu_tanh")), nbytes=tokens * F * 2 * 3)
+    I = moe.w_down.shape[1]
+    gum = torch.randn(tokens, 2 * I, device="cuda").to(bf)
+    logits = torch.randn(tokens, moe.spec.n_experts + 1, device="cuda")
+    wts = kernels.moe_route(logits, moe.spec.n_experts, moe.spec.top_k, True)
+    entry("prefill choice of experts", device_us(lambda: kernels.moe_route(logits, moe.spec.n_experts, moe.spec.top_k, True)),
+          nbytes=tokens * (moe.spec.n_experts + 1) * 8)
+    entry("prefill silu(gate) x up x expert weight", device_us(lambda: kernels.gated_act(gum, "silu", wts, moe.spec.intermediate)), nbytes=tokens * I * 2 * 3)
+    eng.cache.close(slot)
+    slots, ctx = _decode_context(eng, batch, context)
+    recurrences(ctx, batch, batch, False, "decode")
+    kv = ctx.kv(e_par)
+    q1 = torch.randn(batch, left.w_in.shape[0], device="cuda").to(bf)
+    entry("decode attention (window)", device_us(lambda: kernels.attention(
+        q1, q1.shape[1], H, G, D, kv.k, kv.v, kv.table, kv.stride, ctx.tok_pos, ctx.tok_row, window, D ** -0.5, ctx)),
+        nbytes=batch * min(context, window) * 2 * G * D * 2)
+    B.close_sequences(eng, slots)
+
+
+def kernel_times(size: str, tokens: int, batch: int, context: int, peaks: dict, design: str = "mebalorn") -> Dict[str, dict]:
     """Every kernel of the new design beside the like kernel of the Qwen2 decoder: microseconds, the bytes or
     multiply-adds it must move or do, and that as a fraction of the measured peak."""
     from .engine.engine import Engine
@@ -118,9 +199,16 @@ def kernel_times(size: str, tokens: int, batch: int, context: int, peaks: dict) 
             rec.update(tflops_per_s=flops / us / 1e6, frac=flops / us / 1e6 / peaks["bf16_tflops"], bound="bf16")
         out[name] = rec
 
-    for design, cfg in (("mebalorn", mebalorn_config(size)), ("qwen2", qwen2_config(size))):
+    entry.out = out
+    for design, cfg in ((design, DESIGNS[design](size)), ("qwen2", qwen2_config(size))):
         eng = Engine.from_config(config_from_dict(cfg), seed=1, draw_on="cuda", dtype="bfloat16")
         eng.ensure_cache(max(tokens, batch * context) + 64 * batch, max(tokens, context), max_seqs=batch + 1)
+        if design == "kevelorn":
+            kevelorn_kernel_times(eng, size, tokens, batch, context, entry)
+            kernels.check_status(eng.device)
+            del eng
+            torch.cuda.empty_cache()
+            continue
         e_att = next(e for e, s in enumerate(eng.model.plan.schedule) if hasattr(eng.model.layers[s.layer].mixer.spec, "n_heads"))
         att = eng.model.layers[e_att].mixer
         seen = tokens * (tokens + 1) / 2
@@ -180,11 +268,11 @@ def kernel_times(size: str, tokens: int, batch: int, context: int, peaks: dict) 
     return out
 
 
-def throughput(size: str, tokens: int, batch: int, context: int, steps: int = 64) -> Dict[str, dict]:
+def throughput(size: str, tokens: int, batch: int, context: int, steps: int = 64, design: str = "mebalorn") -> Dict[str, dict]:
     """Prefill of one prompt and decode of ``batch`` sequences through the engines' own steps, both designs."""
     from .engine.engine import Engine
     out = {}
-    for design, cfg in (("mebalorn", mebalorn_config(size)), ("qwen2", qwen2_config(size))):
+    for design, cfg in ((design, DESIGNS[design](size)), ("qwen2", qwen2_config(size))):
         eng = Engine.from_config(config_from_dict(cfg), seed=1, draw_on="cuda", dtype="bfloat16")
         pre = B.prefill_device(eng, tokens)
         dec = B.decode_device(eng, batch, context, steps, 4)
@@ -197,16 +285,18 @@ def throughput(size: str, tokens: int, batch: int, context: int, steps: int = 64
     return out
 
 
-def compare(sizes, tokens: int, batch: int, context: int, peaks: dict) -> dict:
+def compare(sizes, tokens: int, batch: int, context: int, peaks: dict, design: str = "mebalorn") -> dict:
     record = {"tokens": tokens, "batch": batch, "context": context, "layers": {s: SIZES[s][5] for s in sizes},
               "widths": {s: dict(zip(("width", "heads", "kv_heads", "head_dim", "ff"), SIZES[s][:5])) for s in sizes}, "sizes": {}}
     for s in sizes:
-        record["sizes"][s] = {"throughput": throughput(s, tokens, batch, context), "kernels": kernel_times(s, tokens, batch, context, peaks)}
+        record["sizes"][s] = {"throughput": throughput(s, tokens, batch, context, design=design),
+                              "kernels": kernel_times(s, tokens, batch, context, peaks, design)}
     return record
 
 
 def main(argv=None) -> None:
     p = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    p.add_argument("--design", default="mebalorn", choices=sorted(DESIGNS))
     p.add_argument("--sizes", default="s,m")
     p.add_argument("--tokens", type=int, default=2048)
     p.add_argument("--batch", type=int, default=8)
@@ -215,7 +305,7 @@ def main(argv=None) -> None:
     p.add_argument("--bf16-tflops", type=float, default=1590.0)
     p.add_argument("--output")
     a = p.parse_args(argv)
-    rec = compare([s for s in a.sizes.split(",") if s], a.tokens, a.batch, a.context, {"hbm_gbs": a.hbm_gbs, "bf16_tflops": a.bf16_tflops})
+    rec = compare([s for s in a.sizes.split(",") if s], a.tokens, a.batch, a.context, {"hbm_gbs": a.hbm_gbs, "bf16_tflops": a.bf16_tflops}, a.design)
     for s, r in rec["sizes"].items():
         for d, t in r["throughput"].items():
             print(f"{s} {d}: prefill {t['prefill_tokens_per_s']:.0f} tok/s ({t['prefill_ms']:.2f} ms), decode {t['decode_tokens_per_s']:.0f} tok/s "

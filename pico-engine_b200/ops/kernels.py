@@ -486,9 +486,10 @@ def set_batch_fused(on: bool) -> bool:
 def linear_fused(a: Optional[torch.Tensor], w: torch.Tensor, bias: Optional[torch.Tensor] = None,
                  out_dtype: Optional[torch.dtype] = None, accumulate_into: Optional[torch.Tensor] = None,
                  norm_of: Optional[torch.Tensor] = None, norm_weight: Optional[torch.Tensor] = None,
-                 eps: float = 0.0) -> torch.Tensor:
+                 eps: float = 0.0, scale: float = 1.0) -> torch.Tensor:
     """a [M <= 64, K] . w [N, K]^T (+ bias); with ``norm_of`` (float32 [M, K]) the operand is
-    RMSNorm(norm_of) with ``norm_weight`` instead of ``a``.  (More than 16 rows: bfloat16 or accumulated results.)"""
+    RMSNorm(norm_of) with ``norm_weight`` instead of ``a``.  (More than 16 rows: bfloat16 or accumulated results.)
+    ``scale`` (up to 16 rows, with ``accumulate_into``): accumulate_into += scale * product."""
     src = norm_of if norm_of is not None else a
     M, K = src.shape
     N = w.shape[0]
@@ -505,6 +506,13 @@ def linear_fused(a: Optional[torch.Tensor], w: torch.Tensor, bias: Optional[torc
     else:
         out = torch.empty(M, N, dtype=out_dtype or torch.bfloat16, device=w.device)
         epilogue = _EPILOGUE_STORE[out.dtype]
+    if scale != 1.0:
+        if M > FUSED_MAX_ROWS or accumulate_into is None:
+            raise KernelError("a scaled sum into the stream is taken for up to 16 rows")
+        check(core().pe_linear_fused_scaled(_ptr(a), _ptr(norm_of), _ptr(norm_weight), 0 if norm_weight is None else _code(norm_weight, "norm_weight"),
+                                            float(eps), w.data_ptr(), _ptr(bias), 0 if bias is None else _code(bias, "bias"), out.data_ptr(),
+                                            epilogue, float(scale), M, N, K, status_ptr(w.device), stream_ptr()), "linear_fused")
+        return out
     fn, name = (core().pe_linear_fused, "linear_fused") if M <= FUSED_MAX_ROWS else (extras().pe_linear_batch, "linear_batch")
     check(fn(_ptr(a), _ptr(norm_of), _ptr(norm_weight), 0 if norm_weight is None else _code(norm_weight, "norm_weight"), float(eps),
              w.data_ptr(), _ptr(bias), 0 if bias is None else _code(bias, "bias"), out.data_ptr(),

@@ -42,6 +42,7 @@ _SIGNATURES = {
     "pe_gemm_tcgen05": [P, P, P, I, P, I, I, I, I, I, P, P],
     "pe_gemm_tcgen05_rope": [P, P, P, I, P, I, I, I, I, I, P, P, P, P, P, P, P, I, I, I, P, P],
     "pe_linear_fused": [P, P, P, I, F, P, P, I, P, I, I, I, I, P, P],
+    "pe_linear_fused_scaled": [P, P, P, I, F, P, P, I, P, I, F, I, I, I, P, P],
     "pe_norm_gate_up_swiglu": [P, P, I, F, P, P, I, I, I, P, P],
     "pe_norm_qkv_rope_store": [P, P, P, I, F, P, P, I, P, I, I, I, I, I, P, P, P, P, P, P, P, I, I, P, P],
     "pe_add_sinusoid": [P, P, P, I, I, P],

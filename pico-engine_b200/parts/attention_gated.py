@@ -7,7 +7,7 @@ from ..cache import CacheNeeds, KVNeed
 from ..config.specs import ConfigError, GatedAttentionSpec, NoPositionSpec, RotaryPairsSpec
 from ..ops import kernels, linear
 from ..weights.loader import ParamSpec
-from .base import Mixer, register_mixer
+from .base import Mixer, first_product, last_product_into, normed_rows, register_mixer
 
 
 def pair_frequencies(spec: RotaryPairsSpec, device) -> torch.Tensor:
@@ -80,12 +80,12 @@ class GatedAttention(Mixer):
         return CacheNeeds(kv=KVNeed(s.n_kv_heads, s.head_dim, s.window,
                                     v_head_dim=None if s.v_head_dim == s.head_dim else s.v_head_dim))
 
-    def gated_heads(self, h, ctx, cache_entry, owns_cache):
-        """The heads' outputs times the gate [T, n_heads * v_head_dim] for normed rows h."""
+    def gated_heads(self, h, ctx, cache_entry, owns_cache, x_norm=None):
+        """The heads' outputs times the gate [T, n_heads * v_head_dim] for normed rows h (or ``x_norm`` = (stream, its norm))."""
         s = self.spec
         q_w, k_w, v_w, o_w = self._widths()
         kv = ctx.kv(cache_entry)
-        proj = linear(h, self.w_in, out_dtype=ctx.dtype)
+        proj = first_product(*normed_rows(h, x_norm, ctx, self.w_in), self.w_in, ctx)
         rot_dims = s.position.dims if isinstance(s.position, RotaryPairsSpec) else 0
         kernels.rotary_norm_store(proj, s.n_heads, s.n_kv_heads, s.head_dim, s.v_head_dim, self.freq, rot_dims, s.qk_unit_norm,
                                   s.norm_eps, ctx.tok_pos, ctx.tok_row, kv.k if owns_cache else None, kv.v if owns_cache else None,
@@ -100,5 +100,9 @@ class GatedAttention(Mixer):
             return a
         return kernels.gated_norm(a, 0, None, s.norm_eps, proj, q_w + k_w + v_w, "sigmoid", ctx.dtype)
 
-    def apply(self, h, ctx, entry, cache_entry, owns_cache, out_dtype=None):
-        return linear(self.gated_heads(h, ctx, cache_entry, owns_cache), self.w_o, out_dtype=out_dtype or ctx.dtype)
+    def apply(self, h, ctx, entry, cache_entry, owns_cache, out_dtype=None, x_norm=None):
+        return linear(self.gated_heads(h, ctx, cache_entry, owns_cache, x_norm), self.w_o, out_dtype=out_dtype or ctx.dtype)
+
+    def add_normed_to(self, x, norm, scale, ctx, entry, cache_entry, owns_cache) -> bool:
+        last_product_into(x, self.gated_heads(None, ctx, cache_entry, owns_cache, (x, norm)), self.w_o, scale, ctx)
+        return True

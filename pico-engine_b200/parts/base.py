@@ -112,6 +112,38 @@ class StepContext:
         return self.cache.state_of(cache_entry)
 
 
+def normed_rows(h, x_norm, ctx, w):
+    """What a part's first product reads: either rows ``h`` that are normed already, or, for a step of few rows in
+    bfloat16 whose weight ``w`` the fused decode product takes, the float32 stream and its RMS norm (``x_norm`` = (x, norm)),
+    which that product applies in its prologue.  Returns (h, norm_of, norm_weight, eps); exactly one of h and norm_of is set."""
+    if x_norm is None:
+        return h, None, None, 0.0
+    from ..ops import kernels
+    from .norm import RMSNorm
+    x, norm = x_norm
+    if ctx.dtype == torch.bfloat16 and type(norm) is RMSNorm and kernels.fused_takes(x.shape[0], w, x):
+        return None, x, norm.weight, norm.eps
+    return norm.forward(x, ctx.dtype), None, None, 0.0
+
+
+def first_product(h, norm_of, norm_weight, eps, w, ctx):
+    """The product of ``normed_rows``'s answer with ``w`` in the step's dtype."""
+    from ..ops import kernels, linear
+    if norm_of is not None:
+        return kernels.linear_fused(None, w, out_dtype=ctx.dtype, norm_of=norm_of, norm_weight=norm_weight, eps=eps)
+    return linear(h, w, out_dtype=ctx.dtype)
+
+
+def last_product_into(x, a, w, scale, ctx):
+    """x += scale * a . w^T on the float32 stream: in the epilogue of the fused decode product where it takes the sizes,
+    else the product's float32 sums followed by the scaled sum."""
+    from ..ops import kernels, linear
+    if a.dtype == torch.bfloat16 and kernels.fused_takes(a.shape[0], w, a):
+        kernels.linear_fused(a, w, accumulate_into=x, scale=scale)
+    else:
+        kernels.scaled_add(x, linear(a, w, out_dtype=torch.float32), scale)
+
+
 class Part:
     def __init__(self, spec: PartSpec, dtype: torch.dtype, device):
         self.spec, self.dtype, self.device = spec, dtype, device

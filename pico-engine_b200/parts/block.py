@@ -69,20 +69,25 @@ def pre_norm(layer: Layer, x, ctx, entry, cache_entry, owns_cache) -> None:
     """x += mixer(norm(x)); x += feed_forward(norm(x))  (pico-engine src/pico_engine/model.py:167-237).  With a
     ``residual_scale`` m other than 1 both sums are x += m * sublayer(norm(x)), formed in float32 from the sublayer's
     output (a part may do the sum itself: ``add_scaled_to``)."""
-    m = layer.spec.residual_scale
+    m = getattr(getattr(layer, "spec", None), "residual_scale", 1.0)
     if m != 1.0:
         from ..ops import kernels
         ctx.settle(x)
-        if layer.mixer is not None:
-            h = layer.mixer_norm.forward(x, ctx.dtype)
-            if hasattr(layer.mixer, "add_scaled_to"):
-                layer.mixer.add_scaled_to(x, h, m, ctx, entry, cache_entry, owns_cache)
+        halves = ((layer.mixer, layer.mixer_norm, (entry, cache_entry, owns_cache)), (layer.feed_forward, layer.feed_forward_norm, ()))
+        for part, norm, where in halves:
+            if part is None:
+                continue
+            # a part may do the whole half itself (the norm in the prologue of its first product, the scaled sum in the
+            # epilogue of its last one, for steps of few rows); it says whether it did
+            fused = getattr(part, "add_normed_to", None)
+            if fused is not None and fused(x, norm, m, ctx, *where):
+                continue
+            h = norm.forward(x, ctx.dtype)
+            if hasattr(part, "add_scaled_to"):
+                part.add_scaled_to(x, h, m, ctx, *where)
             else:
-                wide = {"out_dtype": x.dtype} if getattr(layer.mixer, "takes_out_dtype", False) else {}
-                kernels.scaled_add(x, layer.mixer.apply(h, ctx, entry, cache_entry, owns_cache, **wide).contiguous(), m)
-        if layer.feed_forward is not None:
-            wide = {"out_dtype": x.dtype} if getattr(layer.feed_forward, "takes_out_dtype", False) else {}
-            kernels.scaled_add(x, layer.feed_forward.apply(layer.feed_forward_norm.forward(x, ctx.dtype), ctx, **wide).contiguous(), m)
+                wide = {"out_dtype": x.dtype} if getattr(part, "takes_out_dtype", False) else {}
+                kernels.scaled_add(x, part.apply(h, ctx, *where, **wide).contiguous(), m)
         return
     if layer.mixer is not None:
         if not layer.mixer.takes_pending:

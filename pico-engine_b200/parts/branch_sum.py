@@ -59,6 +59,14 @@ class BranchSum(Mixer):
     def cache_needs(self):
         return self._needs
 
+    def add_normed_to(self, x, norm, scale, ctx, entry, cache_entry, owns_cache) -> bool:
+        """x += scale * mixer(norm(x)); branches that can take the norm into their first product."""
+        if not all(getattr(b, "takes_out_dtype", False) for b in self.branches):
+            return False
+        outs = [b.apply(None, ctx, entry, cache_entry, owns_cache, out_dtype=x.dtype, x_norm=(x, norm)) for b in self.branches]
+        kernels.normed_sum_add(x, outs, self.out_norms, self.spec.norm_eps, scale * self.spec.weight)
+        return True
+
     def add_scaled_to(self, x, h, scale, ctx, entry, cache_entry, owns_cache) -> None:
         """x += scale * mixer(h) for normed rows h."""
         outs = [b.apply(h, ctx, entry, cache_entry, owns_cache, **({"out_dtype": x.dtype} if getattr(b, "takes_out_dtype", False) else {}))

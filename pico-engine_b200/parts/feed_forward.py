@@ -6,7 +6,7 @@ import torch
 from ..config.specs import ConfigError, DenseMLPSpec, GatedMLPSpec, SwiGLUSpec
 from ..ops import kernels, linear
 from ..weights.loader import ParamSpec
-from .base import FeedForward, register_feed_forward
+from .base import FeedForward, first_product, last_product_into, normed_rows, register_feed_forward
 
 
 @register_feed_forward(SwiGLUSpec)
@@ -110,10 +110,17 @@ class GatedMLP(FeedForward):
         from ..ops.library import gated
         gated()                                            # build or load this part's kernels now, loudly
 
-    def apply(self, h, ctx, out_dtype=None):
-        if self.spec.activation == "silu":
+    def _activation(self, h, ctx, x_norm=None):
+        if self.spec.activation == "silu" and x_norm is None:
             from ..ops.linear import gate_up_swiglu
-            act = gate_up_swiglu(h, self.w_gate_up)
-        else:
-            act = kernels.gated_act(linear(h, self.w_gate_up, out_dtype=ctx.dtype), self.spec.activation)
-        return linear(act, self.w_down, out_dtype=out_dtype or ctx.dtype)
+            return gate_up_swiglu(h, self.w_gate_up)
+        gate_up = first_product(*normed_rows(h, x_norm, ctx, self.w_gate_up), self.w_gate_up, ctx)
+        return kernels.gated_act(gate_up, self.spec.activation)
+
+    def apply(self, h, ctx, out_dtype=None):
+        return linear(self._activation(h, ctx), self.w_down, out_dtype=out_dtype or ctx.dtype)
+
+    def add_normed_to(self, x, norm, scale, ctx) -> bool:
+        """x += scale * feed_forward(norm(x)), the norm in the first product and the sum in the last where they take the sizes."""
+        last_product_into(x, self._activation(None, ctx, (x, norm)), self.w_down, scale, ctx)
+        return True

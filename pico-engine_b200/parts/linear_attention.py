@@ -7,7 +7,7 @@ from ..cache import CacheNeeds
 from ..config.specs import ConfigError, LinearAttentionSpec
 from ..ops import kernels, linear
 from ..weights.loader import ParamSpec
-from .base import Mixer, register_mixer
+from .base import Mixer, first_product, last_product_into, normed_rows, register_mixer
 
 
 @register_mixer(LinearAttentionSpec)
@@ -75,14 +75,18 @@ class LinearAttention(Mixer):
         s = self.spec
         return CacheNeeds(kv=None, state_elems=s.n_heads * s.head_dim * s.v_head_dim)
 
-    def gated_output(self, h, ctx, cache_entry):
-        """norm(o_t) * gate [T, heads * v_head_dim] of the step's tokens; the sequences' states move on."""
+    def gated_output(self, h, ctx, cache_entry, x_norm=None):
+        """norm(o_t) * gate [T, heads * v_head_dim] of the step's tokens; the sequences' states move on.  The input is
+        either normed rows ``h`` or ``x_norm`` = (stream, its norm)."""
         s = self.spec
         qk, vo = self._sizes()
-        proj = linear(h, self.w_in, out_dtype=ctx.dtype)
+        rows = normed_rows(h, x_norm, ctx, self.w_in)
+        proj = first_product(*rows, self.w_in, ctx)
         logits = None
         if self.w_a1 is not None:
-            logits = linear(linear(h, self.w_a1, out_dtype=ctx.dtype), self.w_a2, self.b_a2, out_dtype=torch.float32)
+            if rows[0] is None and not kernels.fused_takes(proj.shape[0], self.w_a1, rows[1]):
+                rows = (x_norm[1].forward(x_norm[0], ctx.dtype), None, None, 0.0)
+            logits = linear(first_product(*rows, self.w_a1, ctx), self.w_a2, self.b_a2, out_dtype=torch.float32)
         # sequences that bring many tokens: three passes over chunks; a step of (about) one token each: token after token
         o = kernels.linear_attention(proj, 0, qk, 2 * qk, s.n_heads, s.head_dim, s.v_head_dim, ctx.state(cache_entry),
                                      self.state_offset, ctx.row_first, ctx.row_lens, ctx.slots, chunked=ctx.T > 2 * ctx.B,
@@ -91,5 +95,10 @@ class LinearAttention(Mixer):
         return kernels.gated_norm(o, vo if s.norm_over == "heads" else s.v_head_dim, self.norm, s.norm_eps, proj, 2 * qk + vo,
                                   s.gate_activation, ctx.dtype)
 
-    def apply(self, h, ctx, entry, cache_entry, owns_cache, out_dtype=None):
-        return linear(self.gated_output(h, ctx, cache_entry), self.w_o, out_dtype=out_dtype or ctx.dtype)
+    def apply(self, h, ctx, entry, cache_entry, owns_cache, out_dtype=None, x_norm=None):
+        return linear(self.gated_output(h, ctx, cache_entry, x_norm), self.w_o, out_dtype=out_dtype or ctx.dtype)
+
+    def add_normed_to(self, x, norm, scale, ctx, entry, cache_entry, owns_cache) -> bool:
+        """x += scale * mixer(norm(x)), the norm in the first product and the sum in the last where they take the sizes."""
+        last_product_into(x, self.gated_output(None, ctx, cache_entry, (x, norm)), self.w_o, scale, ctx)
+        return True

@@ -6,7 +6,7 @@ import torch
 from ..config.specs import ConfigError, MixtureSpec
 from ..ops import kernels, linear
 from ..weights.loader import ParamSpec
-from .base import FeedForward, register_feed_forward
+from .base import FeedForward, last_product_into, register_feed_forward
 
 
 @register_feed_forward(MixtureSpec)
@@ -68,9 +68,16 @@ class Mixture(FeedForward):
         logits = linear(h, self.w_router, out_dtype=torch.float32)
         return kernels.moe_route(logits, s.n_experts, s.top_k, s.shared_intermediate is not None)
 
-    def apply(self, h, ctx, out_dtype=None):
+    def _activation(self, h, ctx):
         s = self.spec
         weights = self.routing(h)
         gate_up = linear(h, self.w_gate_up, out_dtype=ctx.dtype)
-        act = kernels.gated_act(gate_up, s.activation, weights, s.intermediate)
-        return linear(act, self.w_down, out_dtype=out_dtype or ctx.dtype)
+        return kernels.gated_act(gate_up, s.activation, weights, s.intermediate)
+
+    def apply(self, h, ctx, out_dtype=None):
+        return linear(self._activation(h, ctx), self.w_down, out_dtype=out_dtype or ctx.dtype)
+
+    def add_normed_to(self, x, norm, scale, ctx) -> bool:
+        """x += scale * mixture(norm(x)); the router reads the normed rows themselves, the sum is the last product's epilogue."""
+        last_product_into(x, self._activation(norm.forward(x, ctx.dtype), ctx), self.w_down, scale, ctx)
+        return True
