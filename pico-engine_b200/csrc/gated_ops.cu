@@ -20,31 +20,33 @@ __device__ __forceinline__ float go_act(float v, int act) {
 // are turned by the angle pos * freq[i]: (u, v) -> (u cos - v sin, v cos + u sin); then (norm != 0) the head is divided
 // by sqrt(mean(head^2) + eps).  The heads are rewritten in place; keys and values also go to their cache pages.
 // A warp a head; a lane keeps its entries of the head in registers (D <= 256).
-template <typename T>
+template <typename T, int NE>
 __global__ void __launch_bounds__(128) rotary_norm_store_kernel(T* qkv, int ld, int H, int G, int D, int Dv, const float* freq, int rot_dims,
                                                                 int norm, float eps, const int* tok_pos, const int* tok_row,
                                                                 T* k_pool, T* v_pool, const int* table, int table_stride, int store) {
     pdl_launch_dependents();
-    pdl_wait();
+    __shared__ float s_cos[128], s_sin[128];                               // the token's angles, the same for all its heads
     const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    pdl_wait();
     T* row = qkv + (size_t)t * ld;
     const int pos = tok_pos[t];
+    for (int i = threadIdx.x; i < rot_dims / 2; i += blockDim.x) sincosf((float)pos * freq[i], &s_sin[i], &s_cos[i]);
     long long page = -1;
     if (store) page = table[(size_t)tok_row[t] * table_stride + pos / PE_PAGE];
+    __syncthreads();
     for (int u = warp; u < H + 2 * G; u += 4) {
         if (u < H + G) {
             T* v = row + (size_t)u * D;
-            float val[8];
+            float val[NE];
             float ss = 0.f;
 #pragma unroll
-            for (int e = 0; e < 8; ++e) {
+            for (int e = 0; e < NE; ++e) {
                 const int d = lane + 32 * e;
                 float f = 0.f;
                 if (d < D) {
                     f = to_f(v[d]);
                     if ((d | 1) < rot_dims) {
-                        float sn, cs;
-                        sincosf((float)pos * freq[d >> 1], &sn, &cs);
+                        const float sn = s_sin[d >> 1], cs = s_cos[d >> 1];
                         const float other = to_f(v[d ^ 1]);
                         f = (d & 1) ? fmaf(f, cs, other * sn) : fmaf(f, cs, -other * sn);
                     }
@@ -56,7 +58,7 @@ __global__ void __launch_bounds__(128) rotary_norm_store_kernel(T* qkv, int ld, 
             __syncwarp();                                                  // every lane has read its partners
             T* dst = (u >= H && store && page >= 0) ? k_pool + (((size_t)page * G + (u - H)) * PE_PAGE + pos % PE_PAGE) * D : nullptr;
 #pragma unroll
-            for (int e = 0; e < 8; ++e) {
+            for (int e = 0; e < NE; ++e) {
                 const int d = lane + 32 * e;
                 if (d < D) {
                     const T o = from_f<T>(val[e] * rstd);
@@ -79,13 +81,14 @@ extern "C" int pe_rotary_norm_store(void* qkv, int dtype, int ld, int T, int H, 
     if (T <= 0) return 0;
     if (D > 256 || rot_dims > D || (rot_dims & 1) || (rot_dims > 0 && !freq) || ld < (H + G) * D + G * Dv) return PE_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == PE_F32)
-        PE_TRY(pe_launch(rotary_norm_store_kernel<float>, T, 128, 0, s, (float*)qkv, ld, H, G, D, Dv, freq, rot_dims, norm, eps, tok_pos,
-                         tok_row, (float*)k_pool, (float*)v_pool, table, table_stride, store));
-    else if (dtype == PE_BF16)
-        PE_TRY(pe_launch(rotary_norm_store_kernel<bf16>, T, 128, 0, s, (bf16*)qkv, ld, H, G, D, Dv, freq, rot_dims, norm, eps, tok_pos,
-                         tok_row, (bf16*)k_pool, (bf16*)v_pool, table, table_stride, store));
-    else return PE_ERR_UNSUPPORTED;
+#define ROT_LAUNCH(TT, NE) PE_TRY(pe_launch(rotary_norm_store_kernel<TT, NE>, T, 128, 0, s, (TT*)qkv, ld, H, G, D, Dv, freq, rot_dims, norm, eps, \
+                                            tok_pos, tok_row, (TT*)k_pool, (TT*)v_pool, table, table_stride, store))
+    if (dtype == PE_F32) {
+        if (D <= 64) ROT_LAUNCH(float, 2); else if (D <= 128) ROT_LAUNCH(float, 4); else ROT_LAUNCH(float, 8);
+    } else if (dtype == PE_BF16) {
+        if (D <= 64) ROT_LAUNCH(bf16, 2); else if (D <= 128) ROT_LAUNCH(bf16, 4); else ROT_LAUNCH(bf16, 8);
+    } else return PE_ERR_UNSUPPORTED;
+#undef ROT_LAUNCH
     PE_LAUNCH_CHECK();
     return 0;
 }
@@ -116,26 +119,69 @@ __global__ void __launch_bounds__(256) gated_norm_kernel(const TI* in, int C, in
     }
 }
 
+// The same for groups of up to 512 channels: a warp a (token, group), eight of them a block, the run kept in registers.
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(256) gated_norm_warp_kernel(const TI* in, int C, int group, const void* weight, int w_dtype, float eps,
+                                                              const TO* gate, int g_ld, int g_off, int gate_act, TO* out, long long runs) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long run = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (run >= runs) return;
+    const int per_row = C / group;
+    const size_t t = (size_t)(run / per_row);
+    const int c0 = (int)(run % per_row) * group;
+    const TI* src = in + t * C + c0;
+    float val[16];
+    float ss = 0.f;
+#pragma unroll
+    for (int e = 0; e < 16; ++e) {
+        const int i = lane + 32 * e;
+        val[e] = i < group ? to_f(src[i]) : 0.f;
+        ss = fmaf(val[e], val[e], ss);
+    }
+    const float rstd = 1.0f / sqrtf(warp_sum(ss) / (float)group + eps);
+#pragma unroll
+    for (int e = 0; e < 16; ++e) {
+        const int i = lane + 32 * e;
+        if (i < group) {
+            float f = val[e] * rstd;
+            if (weight) f *= load_as_f(weight, w_dtype, i);
+            if (gate) f *= go_act(to_f(gate[t * g_ld + g_off + c0 + i]), gate_act);
+            out[t * C + c0 + i] = from_f<TO>(f);
+        }
+    }
+}
+
+template <typename TI, typename TO>
+static int gated_norm_launch(const void* in, int T, int C, int group, const void* weight, int w_dtype, float eps, const void* gate, int g_ld,
+                             int g_off, int gate_act, void* out, cudaStream_t s) {
+    if (group > 0 && group <= 512) {
+        const long long runs = (long long)T * (C / group);
+        PE_TRY(pe_launch(gated_norm_warp_kernel<TI, TO>, (unsigned)((runs + 7) / 8), 256, 0, s, (const TI*)in, C, group, weight, w_dtype, eps,
+                         (const TO*)gate, g_ld, g_off, gate_act, (TO*)out, runs));
+    } else {
+        const int n = group > 0 ? group : C;
+        const int threads = n >= 256 ? 256 : ((n + 31) / 32) * 32;
+        PE_TRY(pe_launch(gated_norm_kernel<TI, TO>, dim3(T, C / n), threads, 0, s, (const TI*)in, C, group, weight, w_dtype, eps,
+                         (const TO*)gate, g_ld, g_off, gate_act, (TO*)out));
+    }
+    PE_LAUNCH_CHECK();
+    return 0;
+}
+
 extern "C" int pe_gated_norm(const void* in, int in_dtype, int T, int C, int group, const void* weight, int w_dtype, float eps,
                              const void* gate, int g_ld, int g_off, int gate_act, void* out, int out_dtype, void* stream) {
     if (T <= 0 || C <= 0) return 0;
     if (group < 0 || (group > 0 && C % group)) return PE_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
-    const int n = group > 0 ? group : C;
-    const dim3 grid(T, C / n);
-    const int threads = n >= 256 ? 256 : ((n + 31) / 32) * 32;
     if (in_dtype == PE_F32 && out_dtype == PE_F32)
-        PE_TRY(pe_launch(gated_norm_kernel<float, float>, grid, threads, 0, s, (const float*)in, C, group, weight, w_dtype, eps,
-                         (const float*)gate, g_ld, g_off, gate_act, (float*)out));
-    else if (in_dtype == PE_F32 && out_dtype == PE_BF16)
-        PE_TRY(pe_launch(gated_norm_kernel<float, bf16>, grid, threads, 0, s, (const float*)in, C, group, weight, w_dtype, eps,
-                         (const bf16*)gate, g_ld, g_off, gate_act, (bf16*)out));
-    else if (in_dtype == PE_BF16 && out_dtype == PE_BF16)
-        PE_TRY(pe_launch(gated_norm_kernel<bf16, bf16>, grid, threads, 0, s, (const bf16*)in, C, group, weight, w_dtype, eps,
-                         (const bf16*)gate, g_ld, g_off, gate_act, (bf16*)out));
-    else return PE_ERR_UNSUPPORTED;
-    PE_LAUNCH_CHECK();
-    return 0;
+        return gated_norm_launch<float, float>(in, T, C, group, weight, w_dtype, eps, gate, g_ld, g_off, gate_act, out, s);
+    if (in_dtype == PE_F32 && out_dtype == PE_BF16)
+        return gated_norm_launch<float, bf16>(in, T, C, group, weight, w_dtype, eps, gate, g_ld, g_off, gate_act, out, s);
+    if (in_dtype == PE_BF16 && out_dtype == PE_BF16)
+        return gated_norm_launch<bf16, bf16>(in, T, C, group, weight, w_dtype, eps, gate, g_ld, g_off, gate_act, out, s);
+    return PE_ERR_UNSUPPORTED;
 }
 
 // ---------------------------------------------------------------- x += scale * sum_i rmsnorm(y_i) * w_i
@@ -162,6 +208,49 @@ __global__ void __launch_bounds__(256) normed_sum_add_kernel(float* x, NormedSum
     }
 }
 
+// float32 branches, W a multiple of 4 and at most 4096: a thread keeps its up to four float4 of every branch in registers
+// between the sums of squares and the result, so every row is read once.
+template <int NB>
+__global__ void __launch_bounds__(256) normed_sum_add_f32x4_kernel(float* x, NormedSumArgs a, int w_dtype, int W, float eps, float scale) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float red[33];
+    const size_t t = blockIdx.x;
+    const int nv = W / 4;
+    float4 val[NB][4];
+    float rstd[NB];
+#pragma unroll
+    for (int b = 0; b < NB; ++b) {
+        const float4* y = reinterpret_cast<const float4*>((const float*)a.y[b] + t * W);
+        float ss = 0.f;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int i = threadIdx.x + 256 * e;
+            val[b][e] = i < nv ? y[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+            ss += val[b][e].x * val[b][e].x + val[b][e].y * val[b][e].y + val[b][e].z * val[b][e].z + val[b][e].w * val[b][e].w;
+        }
+        rstd[b] = 1.0f / sqrtf(block_sum(ss, red) / (float)W + eps);
+    }
+    float4* xr = reinterpret_cast<float4*>(x + t * W);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        const int i = threadIdx.x + 256 * e;
+        if (i < nv) {
+            float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int b = 0; b < NB; ++b) {
+                sum.x += val[b][e].x * rstd[b] * load_as_f(a.w[b], w_dtype, 4 * i + 0);
+                sum.y += val[b][e].y * rstd[b] * load_as_f(a.w[b], w_dtype, 4 * i + 1);
+                sum.z += val[b][e].z * rstd[b] * load_as_f(a.w[b], w_dtype, 4 * i + 2);
+                sum.w += val[b][e].w * rstd[b] * load_as_f(a.w[b], w_dtype, 4 * i + 3);
+            }
+            float4 xv = xr[i];
+            xv.x = fmaf(scale, sum.x, xv.x); xv.y = fmaf(scale, sum.y, xv.y); xv.z = fmaf(scale, sum.z, xv.z); xv.w = fmaf(scale, sum.w, xv.w);
+            xr[i] = xv;
+        }
+    }
+}
+
 extern "C" int pe_normed_sum_add(float* x, const void* y0, const void* y1, const void* y2, const void* y3, int y_dtype,
                                  const void* w0, const void* w1, const void* w2, const void* w3, int w_dtype, int n, int T, int W,
                                  float eps, float scale, void* stream) {
@@ -169,7 +258,12 @@ extern "C" int pe_normed_sum_add(float* x, const void* y0, const void* y1, const
     if (n < 1 || n > 4) return PE_ERR_UNSUPPORTED;
     NormedSumArgs a = {{y0, y1, y2, y3}, {w0, w1, w2, w3}, n};
     cudaStream_t s = (cudaStream_t)stream;
-    if (y_dtype == PE_F32) PE_TRY(pe_launch(normed_sum_add_kernel<float>, T, 256, 0, s, x, a, w_dtype, W, eps, scale));
+    bool aligned = !((uintptr_t)x & 15);
+    for (int b = 0; b < n; ++b) aligned = aligned && !((uintptr_t)a.y[b] & 15);
+    if (y_dtype == PE_F32 && W % 4 == 0 && W <= 4096 && aligned && n <= 2) {
+        if (n == 1) PE_TRY(pe_launch(normed_sum_add_f32x4_kernel<1>, T, 256, 0, s, x, a, w_dtype, W, eps, scale));
+        else PE_TRY(pe_launch(normed_sum_add_f32x4_kernel<2>, T, 256, 0, s, x, a, w_dtype, W, eps, scale));
+    } else if (y_dtype == PE_F32) PE_TRY(pe_launch(normed_sum_add_kernel<float>, T, 256, 0, s, x, a, w_dtype, W, eps, scale));
     else if (y_dtype == PE_BF16) PE_TRY(pe_launch(normed_sum_add_kernel<bf16>, T, 256, 0, s, x, a, w_dtype, W, eps, scale));
     else return PE_ERR_UNSUPPORTED;
     PE_LAUNCH_CHECK();
@@ -237,6 +331,47 @@ __global__ void gated_act_kernel(const T* gu, T* out, int I, int act, const floa
     }
 }
 
+// bfloat16, I a multiple of 8, aligned rows: eight columns a thread with 16-byte accesses.  Sigmoid and tanh come from the
+// special-function unit's 2^x and reciprocal (relative error about 2^-22, far below the bfloat16 rounding of the result).
+__device__ __forceinline__ float go_sigmoid_fast(float v) {
+    float e, r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-1.4426950408889634f * v));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+    return r;
+}
+__device__ __forceinline__ float go_act_fast(float v, int act) {
+    if (act == 2) return v * go_sigmoid_fast(v);
+    if (act == 3) return v * go_sigmoid_fast(1.5957691216057308f * (v + 0.044715f * v * v * v));   // 0.5 v (1 + tanh(u)) = v sigmoid(2u)
+    if (act == 1) return go_sigmoid_fast(v);
+    return v;
+}
+__global__ void gated_act_bf16x8_kernel(const bf16* gu, bf16* out, int I, int act, const float* colw, int group, int n_groups, size_t units) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int per_row = I / 8;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < units; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = idx / per_row, c = (idx % per_row) * 8;
+        const uint4 g = *reinterpret_cast<const uint4*>(gu + t * 2 * I + c), u = *reinterpret_cast<const uint4*>(gu + t * 2 * I + I + c);
+        const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g);
+        const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u);
+        uint4 o;
+        __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 gf = __bfloat1622float2(g2[e]), uf = __bfloat1622float2(u2[e]);
+            float a = go_act_fast(gf.x, act) * uf.x, b = go_act_fast(gf.y, act) * uf.y;
+            if (colw) {
+                const float wa = colw[t * n_groups + min((int)((c + 2 * e) / group), n_groups - 1)];
+                const float wb = colw[t * n_groups + min((int)((c + 2 * e + 1) / group), n_groups - 1)];
+                a = wa == 0.f ? 0.f : a * wa;
+                b = wb == 0.f ? 0.f : b * wb;
+            }
+            o2[e] = __floats2bfloat162_rn(a, b);
+        }
+        *reinterpret_cast<uint4*>(out + t * I + c) = o;
+    }
+}
+
 extern "C" int pe_gated_act(const void* gu, void* out, int dtype, int T, int I, int act, const float* colw, int group, int n_groups,
                             void* stream) {
     if (T <= 0 || I <= 0) return 0;
@@ -244,6 +379,13 @@ extern "C" int pe_gated_act(const void* gu, void* out, int dtype, int T, int I, 
     const size_t total = (size_t)T * I;
     const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
     cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == PE_BF16 && I % 8 == 0 && !(((uintptr_t)gu | (uintptr_t)out) & 15)) {
+        const size_t units = total / 8;
+        const int b8 = (int)((units + 255) / 256 < 148 * 16 ? (units + 255) / 256 : 148 * 16);
+        PE_TRY(pe_launch(gated_act_bf16x8_kernel, b8, 256, 0, s, (const bf16*)gu, (bf16*)out, I, act, colw, group, n_groups, units));
+        PE_LAUNCH_CHECK();
+        return 0;
+    }
     if (dtype == PE_F32) PE_TRY(pe_launch(gated_act_kernel<float>, blocks, 256, 0, s, (const float*)gu, (float*)out, I, act, colw, group, n_groups, total));
     else if (dtype == PE_BF16) PE_TRY(pe_launch(gated_act_kernel<bf16>, blocks, 256, 0, s, (const bf16*)gu, (bf16*)out, I, act, colw, group, n_groups, total));
     else return PE_ERR_UNSUPPORTED;
@@ -256,14 +398,7 @@ extern "C" int pe_gated_act(const void* gu, void* out, int dtype, int T, int I, 
 // every token uses.  weights [T, E + extra] float32: the softmax over the `top` largest logits at their places, zero at
 // the others (of equal logits the lower index is taken first); the extra column holds sigmoid(logit).  ids [T, top] int32
 // (or null) receives the chosen experts, largest logit first.  A warp a token.
-__global__ void __launch_bounds__(128) moe_route_kernel(const float* logits, int ld, int E, int top, int extra, float* weights,
-                                                        int* ids, int T) {
-    pdl_launch_dependents();
-    pdl_wait();
-    const int t = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    if (t >= T) return;
-    const float* z = logits + (size_t)t * ld;
-    float* w = weights + (size_t)t * (E + extra);
+__device__ __forceinline__ void moe_choose(const float* z, int E, int top, int extra, float* w, int* ids, int lane) {
     for (int e = lane; e < E; e += 32) w[e] = 0.f;
     if (extra && lane == 0) w[E] = go_sigmoid(z[E]);
     __syncwarp();
@@ -288,11 +423,57 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* logits, int
         if (k == 0) zmax = best;
         const float p = expf(best - zmax);
         sum += p;
-        if (lane == 0) { w[at] = p; if (ids) ids[(size_t)t * top + k] = at; }
+        if (lane == 0) { w[at] = p; if (ids) ids[k] = at; }
     }
     __syncwarp();
     const float inv = 1.0f / sum;
     for (int e = lane; e < E; e += 32) w[e] *= inv;
+}
+
+__global__ void __launch_bounds__(128) moe_route_kernel(const float* logits, int ld, int E, int top, int extra, float* weights,
+                                                        int* ids, int T) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (t >= T) return;
+    moe_choose(logits + (size_t)t * ld, E, top, extra, weights + (size_t)t * (E + extra), ids ? ids + (size_t)t * top : nullptr, lane);
+}
+
+// The same from the float32 residual stream: the logits are router[e] . (x * rsqrt(mean(x^2) + eps) * norm_w), formed in float32
+// by the token's warp (the RMS norm in front of the router is part of this kernel), for up to MR_MAX_E experts (+ the extra row).
+#define MR_MAX_E 256
+__global__ void __launch_bounds__(128) moe_route_stream_kernel(const float* x, const void* norm_w, int nw_dtype, float eps,
+                                                               const float* router, int K, int E, int top, int extra,
+                                                               float* weights, int* ids, int T) {
+    pdl_launch_dependents();
+    __shared__ float z[4][MR_MAX_E + 1];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * 4 + warp;
+    pdl_wait();
+    if (t >= T) return;
+    const float* row = x + (size_t)t * K;
+    float ss = 0.f;
+    for (int k = lane; k < K; k += 32) ss = fmaf(row[k], row[k], ss);
+    const float rstd = 1.0f / sqrtf(warp_sum(ss) / (float)K + eps);
+    for (int e = 0; e < E + extra; ++e) {
+        const float* w = router + (size_t)e * K;
+        float acc = 0.f;
+        for (int k = lane; k < K; k += 32) acc = fmaf(row[k] * load_as_f(norm_w, nw_dtype, k), w[k], acc);
+        acc = warp_sum(acc);
+        if (lane == 0) z[warp][e] = acc * rstd;
+    }
+    __syncwarp();
+    moe_choose(z[warp], E, top, extra, weights + (size_t)t * (E + extra), ids ? ids + (size_t)t * top : nullptr, lane);
+}
+
+extern "C" int pe_moe_route_stream(const float* x, const void* norm_w, int nw_dtype, float eps, const float* router, int K, int E,
+                                   int top, int extra, float* weights, int* ids, int T, void* stream) {
+    if (T <= 0) return 0;
+    if (E <= 0 || E > MR_MAX_E || top <= 0 || top > E || K <= 0) return PE_ERR_UNSUPPORTED;
+    PE_TRY(pe_launch(moe_route_stream_kernel, (T + 3) / 4, 128, 0, (cudaStream_t)stream, x, norm_w, nw_dtype, eps, router, K, E, top, extra,
+                     weights, ids, T));
+    PE_LAUNCH_CHECK();
+    return 0;
 }
 
 extern "C" int pe_moe_route(const float* logits, int ld, int E, int top, int extra, float* weights, int* ids, int T, void* stream) {

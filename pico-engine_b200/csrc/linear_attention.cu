@@ -47,7 +47,20 @@ struct LAArgs {
     int max_chunks;
 };
 
-__device__ __forceinline__ float la_act(float v, int act) { return act == 1 ? v / (1.0f + expf(-v)) : v; }
+// silu of a projection.  FAST (the bfloat16 engine, whose projections carry 8 bits): 2^x and the reciprocal from the
+// special-function unit, relative error about 2^-22; else the exact routines.  A block applies it to every q and k entry of
+// its head for each of its tokens, so its cost is paid once per 32 columns of the state.
+template <bool FAST>
+__device__ __forceinline__ float la_act(float v, int act) {
+    if (act != 1) return v;
+    if (FAST) {
+        float e, r;
+        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-1.4426950408889634f * v));
+        asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+        return v * r;
+    }
+    return v / (1.0f + expf(-v));
+}
 
 // a = sigmoid(z)^(inv_tau), through the logarithm: -softplus(-z) * inv_tau
 __device__ __forceinline__ float la_channel_decay(float z, float inv_tau) {
@@ -78,6 +91,7 @@ __global__ void __launch_bounds__(LA_THREADS) la_walk_kernel(LAArgs a) {
     pdl_launch_dependents();
     pdl_wait();
     constexpr int DP = R * LA_DS;                       // rows the block's threads cover (D rounded up)
+    constexpr bool FAST = sizeof(T) == 2;
     __shared__ __align__(16) float sq[LA_GROUP][DP];
     __shared__ __align__(16) float sk[LA_GROUP][DP];
     __shared__ __align__(16) float sa[PER_CHANNEL ? LA_GROUP : 1][PER_CHANNEL ? DP : 4];
@@ -112,33 +126,45 @@ __global__ void __launch_bounds__(LA_THREADS) la_walk_kernel(LAArgs a) {
     const T* proj = (const T*)a.proj;
     const TZ* zp = (const TZ*)a.z;
 
+    // A group's q, k, a and v are fetched into registers while the group before it is walked, and go to shared memory
+    // (activations, scale and the decay's exponentials applied on the way) when that group is done.
+    constexpr int NQ = LA_GROUP * DP / LA_THREADS;       // entries of q (and of k, of a) a thread fetches for a group
+    float fq[NQ], fk[NQ], fa[PER_CHANNEL ? NQ : 1], fv = 0.f;
+    auto fetch = [&](int g0) {
+        const int ng = min(LA_GROUP, count - g0);
+#pragma unroll
+        for (int n = 0; n < NQ; ++n) {
+            const int i = tid + n * LA_THREADS, tb = i / DP, d = i % DP;
+            const size_t t = (size_t)(first + g0 + tb);
+            const bool on = tb < ng && d < D;
+            fq[n] = on ? to_f(proj[t * a.ld + a.q_off + h * D + d]) : 0.f;
+            fk[n] = on ? to_f(proj[t * a.ld + a.k_off + h * D + d]) : 0.f;
+            if constexpr (PER_CHANNEL) fa[n] = on ? to_f(zp[t * a.z_ld + h * D + d]) : 0.f;
+        }
+        const int tb = tid / LA_COLS, c = blockIdx.z * LA_COLS + jl;
+        fv = (tb < ng && c < Dv) ? to_f(proj[(size_t)(first + g0 + tb) * a.ld + a.v_off + h * Dv + c]) : 0.f;
+    };
+    fetch(0);
     for (int g0 = 0; g0 < count; g0 += LA_GROUP) {
         const int ng = min(LA_GROUP, count - g0);
         __syncthreads();                                 // the last group's reads of shared memory are done
-        for (int i = tid; i < ng * DP; i += LA_THREADS) {
-            const int tb = i / DP, d = i % DP;
-            const size_t t = (size_t)(first + g0 + tb);
-            float q = 0.f, k = 0.f, dec = 0.f;
-            if (d < D) {
-                q = la_act(to_f(proj[t * a.ld + a.q_off + h * D + d]), a.act_qk) * a.q_scale;
-                k = la_act(to_f(proj[t * a.ld + a.k_off + h * D + d]), a.act_qk);
-                if constexpr (PER_CHANNEL) dec = la_channel_decay(to_f(zp[t * a.z_ld + h * D + d]), a.inv_tau);
-            }
-            sq[tb][d] = q; sk[tb][d] = k;
-            if constexpr (PER_CHANNEL) sa[tb][d] = dec;
+#pragma unroll
+        for (int n = 0; n < NQ; ++n) {
+            const int i = tid + n * LA_THREADS, tb = i / DP, d = i % DP;
+            const bool on = tb < ng && d < D;
+            sq[tb][d] = on ? la_act<FAST>(fq[n], a.act_qk) * a.q_scale : 0.f;
+            sk[tb][d] = on ? la_act<FAST>(fk[n], a.act_qk) : 0.f;
+            if constexpr (PER_CHANNEL) sa[tb][d] = on ? la_channel_decay(fa[n], a.inv_tau) : 0.f;
         }
-        for (int i = tid; i < ng * LA_COLS; i += LA_THREADS) {
-            const int tb = i / LA_COLS, c = blockIdx.z * LA_COLS + (i % LA_COLS);
-            const size_t t = (size_t)(first + g0 + tb);
-            sv[tb][i % LA_COLS] = c < Dv ? la_act(to_f(proj[t * a.ld + a.v_off + h * Dv + c]), a.act_v) : 0.f;
-        }
+        sv[tid / LA_COLS][jl] = la_act<FAST>(fv, a.act_v);
         __syncthreads();
+        if (g0 + LA_GROUP < count) fetch(g0 + LA_GROUP);
         if (MODE == 1 && tid < D) {
             for (int tb = 0; tb < ng; ++tb) { if constexpr (PER_CHANNEL) A *= sa[tb][tid]; else A *= hd; }
         }
-        for (int tb = 0; tb < ng; ++tb) {
+        auto token = [&](const int tb) {
             const float v = sv[tb][jl];
-            float acc = 0.f;
+            float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;          // four chains, so that no sum waits for the one before it
 #pragma unroll
             for (int r = 0; r < R; r += 4) {
                 const float4 q4 = *reinterpret_cast<const float4*>(&sq[tb][d0 + r]);
@@ -150,11 +176,18 @@ __global__ void __launch_bounds__(LA_THREADS) la_walk_kernel(LAArgs a) {
                 S[r + 2] = fmaf(a4.z, S[r + 2], k4.z * v);
                 S[r + 3] = fmaf(a4.w, S[r + 3], k4.w * v);
                 if (MODE != 1) {
-                    acc = fmaf(S[r + 0], q4.x, acc); acc = fmaf(S[r + 1], q4.y, acc);
-                    acc = fmaf(S[r + 2], q4.z, acc); acc = fmaf(S[r + 3], q4.w, acc);
+                    acc0 = fmaf(S[r + 0], q4.x, acc0); acc1 = fmaf(S[r + 1], q4.y, acc1);
+                    acc2 = fmaf(S[r + 2], q4.z, acc2); acc3 = fmaf(S[r + 3], q4.w, acc3);
                 }
             }
+            const float acc = (acc0 + acc1) + (acc2 + acc3);
             if (MODE != 1) part[tb][ds][jl] = acc;
+        };
+        if (ng == LA_GROUP) {                            // a full group: constant addresses, no loop
+#pragma unroll
+            for (int tb = 0; tb < LA_GROUP; ++tb) token(tb);
+        } else {
+            for (int tb = 0; tb < ng; ++tb) token(tb);
         }
         if (MODE != 1) {
             __syncthreads();

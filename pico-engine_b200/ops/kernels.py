@@ -1049,3 +1049,21 @@ def moe_route(logits: torch.Tensor, n_experts: int, top_k: int, extra: bool, ids
     check(gated().pe_moe_route(logits.data_ptr(), cols, n_experts, top_k, 1 if extra else 0, out.data_ptr(), _ptr(ids), T,
                                stream_ptr()), "moe_route")
     return out
+
+
+MOE_ROUTE_STREAM_MAX_EXPERTS = 256      # MR_MAX_E of csrc/gated_ops.cu
+
+
+def moe_route_stream(x: torch.Tensor, norm_weight: torch.Tensor, eps: float, router: torch.Tensor, n_experts: int, top_k: int,
+                     extra: bool, ids: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``moe_route`` of the logits router . RMSNorm(x): x float32 [T, K] is the residual stream, ``norm_weight`` [K] the norm's
+    weight, ``router`` float32 [E (+ 1), K]; norm, logits and choice are one kernel, all in float32 (up to 256 experts)."""
+    T, K = x.shape
+    cols = n_experts + (1 if extra else 0)
+    _need(x, "x", torch.float32); _need(norm_weight, "norm_weight", None, (K,)); _need(router, "router", torch.float32, (cols, K))
+    if ids is not None:
+        _need(ids, "ids", torch.int32, (T, top_k))
+    out = torch.empty(T, cols, dtype=torch.float32, device=x.device)
+    check(gated().pe_moe_route_stream(x.data_ptr(), norm_weight.data_ptr(), _code(norm_weight, "norm_weight"), float(eps), router.data_ptr(),
+                                      K, n_experts, top_k, 1 if extra else 0, out.data_ptr(), _ptr(ids), T, stream_ptr()), "moe_route_stream")
+    return out

@@ -71,6 +71,7 @@ _GATED_SIGNATURES = {
     "pe_add_rows": [P, P, P, I, I, I, P],
     "pe_gated_act": [P, P, I, I, I, I, P, I, I, P],
     "pe_moe_route": [P, I, I, I, I, P, P, I, P],
+    "pe_moe_route_stream": [P, P, I, F, P, I, I, I, I, P, P, I, P],
 }
 
 _EXTRA_SIGNATURES = {

@@ -6,7 +6,7 @@ import torch
 from ..config.specs import ConfigError, MixtureSpec
 from ..ops import kernels, linear
 from ..weights.loader import ParamSpec
-from .base import FeedForward, last_product_into, register_feed_forward
+from .base import FeedForward, first_product, last_product_into, normed_rows, register_feed_forward
 
 
 @register_feed_forward(MixtureSpec)
@@ -68,16 +68,26 @@ class Mixture(FeedForward):
         logits = linear(h, self.w_router, out_dtype=torch.float32)
         return kernels.moe_route(logits, s.n_experts, s.top_k, s.shared_intermediate is not None)
 
-    def _activation(self, h, ctx):
+    def _activation(self, h, ctx, x_norm=None):
         s = self.spec
-        weights = self.routing(h)
-        gate_up = linear(h, self.w_gate_up, out_dtype=ctx.dtype)
+        from .norm import RMSNorm
+        if x_norm is not None and type(x_norm[1]) is RMSNorm and s.n_experts <= kernels.MOE_ROUTE_STREAM_MAX_EXPERTS:
+            # the router reads the float32 stream itself (its norm is part of the routing kernel): the same logits however
+            # the step is cut, and the gate/up product may take the norm into its prologue
+            x, norm = x_norm
+            weights = kernels.moe_route_stream(x, norm.weight, norm.eps, self.w_router, s.n_experts, s.top_k, s.shared_intermediate is not None)
+            gate_up = first_product(*normed_rows(None, x_norm, ctx, self.w_gate_up), self.w_gate_up, ctx)
+        else:
+            if h is None:
+                h = x_norm[1].forward(x_norm[0], ctx.dtype)
+            weights = self.routing(h)
+            gate_up = linear(h, self.w_gate_up, out_dtype=ctx.dtype)
         return kernels.gated_act(gate_up, s.activation, weights, s.intermediate)
 
     def apply(self, h, ctx, out_dtype=None):
         return linear(self._activation(h, ctx), self.w_down, out_dtype=out_dtype or ctx.dtype)
 
     def add_normed_to(self, x, norm, scale, ctx) -> bool:
-        """x += scale * mixture(norm(x)); the router reads the normed rows themselves, the sum is the last product's epilogue."""
-        last_product_into(x, self._activation(norm.forward(x, ctx.dtype), ctx), self.w_down, scale, ctx)
+        """x += scale * mixture(norm(x)); the sum is the last product's epilogue where it takes the sizes."""
+        last_product_into(x, self._activation(None, ctx, (x, norm)), self.w_down, scale, ctx)
         return True

@@ -255,12 +255,13 @@ def test_recurrence_keeps_a_key_from_far_back(far):
 
 # ------------------------------------------------------------------ rotation, unit norm and the cache write; the window
 
-def test_rotation_norm_and_store():
+@pytest.mark.parametrize("D", [24, 80, 200])
+def test_rotation_norm_and_store(D):
     from pico_engine.ops import kernels
-    H, G, D, Dv, n = 3, 1, 24, 40, 70
+    H, G, Dv, n = 3, 1, 40, 70
     g = torch.Generator().manual_seed(3)
     for dtype, tol in ((torch.float32, 2e-6), (torch.bfloat16, 1e-2)):
-        for dims, norm in ((24, True), (8, True), (0, True), (16, False)):
+        for dims, norm in ((D, True), (8, True), (0, True), (16, False)):
             row = torch.randn(n, H * D + G * D + G * Dv + 5, generator=g).to(dtype)
             pos = torch.arange(100, 100 + n, dtype=torch.int32)
             freq = (50.0 ** (-2.0 * torch.arange(dims // 2, dtype=torch.float64) / max(dims, 1)) / 3.0).float()
@@ -348,10 +349,10 @@ def test_gated_norm_kernel(dtype):
         assert (got - want).abs().max() < tol * max(1.0, float(want.abs().max()))
 
 
-def test_branch_sum_scaled_add_and_stream_vectors():
+@pytest.mark.parametrize("T,W", [(11, 50), (5, 72), (3, 1100)])          # widths that are and are not multiples of 4, below and above 1024
+def test_branch_sum_scaled_add_and_stream_vectors(T, W):
     from pico_engine.ops import kernels
     g = torch.Generator().manual_seed(2)
-    T, W = 11, 50
     x = torch.randn(T, W, generator=g)
     for dt in (torch.float32, torch.bfloat16):
         ys = [(torch.randn(T, W, generator=g) * s).to(dt) for s in (1.0, 30.0, 0.01)]
@@ -388,6 +389,28 @@ def test_expert_choice(E, top, extra):
         assert sorted(torch.nonzero(got[t, :E]).view(-1).tolist()) == sorted(order)
         if extra:
             assert abs(float(got[t, E]) - 1 / (1 + math.exp(-float(z[t, E])))) < 1e-6
+
+
+@pytest.mark.parametrize("E,top,extra,K", [(8, 4, True, 72), (3, 1, False, 50), (40, 5, True, 130)])
+def test_expert_choice_from_the_stream(E, top, extra, K):
+    """Norm, router product and choice in one kernel against the plain norm and router."""
+    from pico_engine.ops import kernels
+    g = torch.Generator().manual_seed(K)
+    T = 21
+    x = torch.randn(T, K, generator=g) * 3
+    nw = 1 + 0.2 * torch.randn(K, generator=g)
+    router = torch.randn(E + (1 if extra else 0), K, generator=g) * 3 * K ** -0.5
+    ids = torch.zeros(T, top, dtype=torch.int32).cuda()
+    got = kernels.moe_route_stream(x.cuda(), nw.cuda(), 1e-3, router.cuda(), E, top, extra, ids).cpu()
+    z = plain.lin(router.double(), plain.norm_plain(x.double(), nw.double(), 1e-3))
+    for t in range(T):
+        order = sorted(range(E), key=lambda e: -float(z[t, e]))[:top]
+        assert ids[t].tolist() == order
+        want = torch.zeros(E, dtype=torch.float64)
+        want[order] = torch.softmax(z[t, order], 0)
+        assert (got[t, :E] - want).abs().max() < 1e-5
+        if extra:
+            assert abs(float(got[t, E]) - float(plain.sigmoid(z[t, E]))) < 1e-5
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
