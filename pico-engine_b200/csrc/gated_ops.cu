@@ -21,7 +21,7 @@ __device__ __forceinline__ float go_act(float v, int act) {
 // by sqrt(mean(head^2) + eps).  The heads are rewritten in place; keys and values also go to their cache pages.
 // A warp a head; a lane keeps its entries of the head in registers (D <= 256).
 template <typename T, int NE>
-__global__ void __launch_bounds__(128) rotary_norm_store_kernel(T* qkv, int ld, int H, int G, int D, int Dv, const float* freq, int rot_dims,
+__global__ void __launch_bounds__(256) rotary_norm_store_kernel(T* qkv, int ld, int H, int G, int D, int Dv, const float* freq, int rot_dims,
                                                                 int norm, float eps, const int* tok_pos, const int* tok_row,
                                                                 T* k_pool, T* v_pool, const int* table, int table_stride, int store) {
     pdl_launch_dependents();
@@ -34,7 +34,7 @@ __global__ void __launch_bounds__(128) rotary_norm_store_kernel(T* qkv, int ld, 
     long long page = -1;
     if (store) page = table[(size_t)tok_row[t] * table_stride + pos / PE_PAGE];
     __syncthreads();
-    for (int u = warp; u < H + 2 * G; u += 4) {
+    for (int u = warp; u < H + 2 * G; u += (int)(blockDim.x >> 5)) {
         if (u < H + G) {
             T* v = row + (size_t)u * D;
             float val[NE];
@@ -81,7 +81,8 @@ extern "C" int pe_rotary_norm_store(void* qkv, int dtype, int ld, int T, int H, 
     if (T <= 0) return 0;
     if (D > 256 || rot_dims > D || (rot_dims & 1) || (rot_dims > 0 && !freq) || ld < (H + G) * D + G * Dv) return PE_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
-#define ROT_LAUNCH(TT, NE) PE_TRY(pe_launch(rotary_norm_store_kernel<TT, NE>, T, 128, 0, s, (TT*)qkv, ld, H, G, D, Dv, freq, rot_dims, norm, eps, \
+    const int threads = H + 2 * G > 16 ? 256 : 128;                        // a warp walks at most about four heads
+#define ROT_LAUNCH(TT, NE) PE_TRY(pe_launch(rotary_norm_store_kernel<TT, NE>, T, threads, 0, s, (TT*)qkv, ld, H, G, D, Dv, freq, rot_dims, norm, eps, \
                                             tok_pos, tok_row, (TT*)k_pool, (TT*)v_pool, table, table_stride, store))
     if (dtype == PE_F32) {
         if (D <= 64) ROT_LAUNCH(float, 2); else if (D <= 128) ROT_LAUNCH(float, 4); else ROT_LAUNCH(float, 8);
@@ -153,6 +154,59 @@ __global__ void __launch_bounds__(256) gated_norm_warp_kernel(const TI* in, int 
     }
 }
 
+// float32 rows in, bfloat16 out and gate, group a multiple of 4 and all rows aligned: four channels a lane with 16-byte reads of the
+// row and 8-byte reads and writes of gate and result; the run stays in registers between the sum of squares and the result.
+// WARP: a warp a run of up to 512 channels, eight runs a block; else a block a run of up to 4096 channels.
+__device__ __forceinline__ void gn_store4(bf16* out, const bf16* gate, float4 f, int gate_act) {
+    if (gate) {
+        const uint2 g = *reinterpret_cast<const uint2*>(gate);
+        const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g);
+        const float2 a = __bfloat1622float2(g2[0]), b = __bfloat1622float2(g2[1]);
+        f.x *= go_act(a.x, gate_act); f.y *= go_act(a.y, gate_act); f.z *= go_act(b.x, gate_act); f.w *= go_act(b.y, gate_act);
+    }
+    uint2 o;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+    o2[0] = __floats2bfloat162_rn(f.x, f.y); o2[1] = __floats2bfloat162_rn(f.z, f.w);
+    *reinterpret_cast<uint2*>(out) = o;
+}
+
+template <bool WARP>
+__global__ void __launch_bounds__(256) gated_norm_x4_kernel(const float* in, int C, int group, const void* weight, int w_dtype, float eps,
+                                                            const bf16* gate, int g_ld, int g_off, int gate_act, bf16* out, long long runs) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float red[33];
+    const long long run = WARP ? (long long)blockIdx.x * 8 + (threadIdx.x >> 5) : (long long)blockIdx.x;
+    if (WARP && run >= runs) return;
+    const int lane = WARP ? (threadIdx.x & 31) : threadIdx.x, step = WARP ? 32 : 256;
+    const int per_row = C / group, nv = group / 4;
+    const size_t t = (size_t)(run / per_row);
+    const int c0 = (int)(run % per_row) * group;
+    const float4* src = reinterpret_cast<const float4*>(in + t * C + c0);
+    float4 val[4];
+    float ss = 0.f;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        const int i = lane + step * e;
+        val[e] = i < nv ? src[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        ss += val[e].x * val[e].x + val[e].y * val[e].y + val[e].z * val[e].z + val[e].w * val[e].w;
+    }
+    const float total = WARP ? warp_sum(ss) : block_sum(ss, red);
+    const float rstd = 1.0f / sqrtf(total / (float)group + eps);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        const int i = lane + step * e;
+        if (i < nv) {
+            float4 f = make_float4(val[e].x * rstd, val[e].y * rstd, val[e].z * rstd, val[e].w * rstd);
+            if (weight) {
+                f.x *= load_as_f(weight, w_dtype, 4 * i); f.y *= load_as_f(weight, w_dtype, 4 * i + 1);
+                f.z *= load_as_f(weight, w_dtype, 4 * i + 2); f.w *= load_as_f(weight, w_dtype, 4 * i + 3);
+            }
+            gn_store4(out + t * C + c0 + 4 * i, gate ? gate + t * g_ld + g_off + c0 + 4 * i : nullptr, f, gate_act);
+        }
+    }
+}
+
 template <typename TI, typename TO>
 static int gated_norm_launch(const void* in, int T, int C, int group, const void* weight, int w_dtype, float eps, const void* gate, int g_ld,
                              int g_off, int gate_act, void* out, cudaStream_t s) {
@@ -177,6 +231,18 @@ extern "C" int pe_gated_norm(const void* in, int in_dtype, int T, int C, int gro
     cudaStream_t s = (cudaStream_t)stream;
     if (in_dtype == PE_F32 && out_dtype == PE_F32)
         return gated_norm_launch<float, float>(in, T, C, group, weight, w_dtype, eps, gate, g_ld, g_off, gate_act, out, s);
+    if (in_dtype == PE_F32 && out_dtype == PE_BF16 && group > 0 && group % 4 == 0 && group <= 4096 && g_ld % 4 == 0 && g_off % 4 == 0 &&
+        !((uintptr_t)in & 15) && !((uintptr_t)out & 7) && !((uintptr_t)gate & 7)) {
+        const long long runs = (long long)T * (C / group);
+        if (group <= 512)
+            PE_TRY(pe_launch(gated_norm_x4_kernel<true>, (unsigned)((runs + 7) / 8), 256, 0, s, (const float*)in, C, group, weight, w_dtype, eps,
+                             (const bf16*)gate, g_ld, g_off, gate_act, (bf16*)out, runs));
+        else
+            PE_TRY(pe_launch(gated_norm_x4_kernel<false>, (unsigned)runs, 256, 0, s, (const float*)in, C, group, weight, w_dtype, eps,
+                             (const bf16*)gate, g_ld, g_off, gate_act, (bf16*)out, runs));
+        PE_LAUNCH_CHECK();
+        return 0;
+    }
     if (in_dtype == PE_F32 && out_dtype == PE_BF16)
         return gated_norm_launch<float, bf16>(in, T, C, group, weight, w_dtype, eps, gate, g_ld, g_off, gate_act, out, s);
     if (in_dtype == PE_BF16 && out_dtype == PE_BF16)

@@ -103,6 +103,14 @@ def test_mixed_steps(models, name, dtype):
     check(models, name, dtype, replay.mixed(reqs), reqs, "mixed")
 
 
+@pytest.mark.parametrize("name,dtype", [("K1", "float32"), ("K1", "bfloat16"), ("K3", "bfloat16"), ("K4", "float32")])
+def test_batches_of_more_rows_than_the_decode_products_fuse(models, name, dtype):
+    """Twenty short requests start together and are decoded together: steps of 17 and more rows take the products and the
+    residual sums that prompts take, and the recurrence walks twenty sequences side by side."""
+    reqs = requests_for(CONFIGS[name], [3 + (7 * i) % 23 for i in range(20)], 13)
+    check(models, name, dtype, replay.batched(reqs, 20, 0.5), reqs, "twenty rows")
+
+
 @pytest.mark.parametrize("name", ["K1", "K2"])
 def test_long_decoding(models, name):
     """300 tokens one by one from a one-token prompt: windows, pages given back, and states over many steps."""
@@ -327,26 +335,53 @@ def test_window_edge_in_prompt_and_decoding(models, name, dtype):
                     assert (o[p - a].min() > 90.0) == seen and (o[p - a].max() < 10.0) == (not seen), (key_at, p, seen, o[p - a].min(), o[p - a].max())
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("D", [32, 48])
+def test_a_window_of_one_sees_only_the_token_itself(dtype, D):
+    from pico_engine.ops import kernels
+    dt = DTYPES[dtype]
+    H, G, n = 4, 2, 140
+    g = torch.Generator().manual_seed(D)
+    q, k, v = torch.randn(n, H, D, generator=g), torch.randn(n, G, D, generator=g), torch.randn(n, G, D, generator=g).to(dt).float()
+    pages = (n + 63) // 64
+    kp, vp = torch.zeros(pages + 1, G, 64, D, dtype=dt).cuda(), torch.zeros(pages + 1, G, 64, D, dtype=dt).cuda()
+    for p in range(n):
+        kp[1 + p // 64, :, p % 64] = k[p].to(dt).cuda(); vp[1 + p // 64, :, p % 64] = v[p].to(dt).cuda()
+    table = torch.arange(1, pages + 1, dtype=torch.int32).view(1, -1).cuda()
+    for spans in ([(0, n)], [(p, p + 1) for p in (0, 1, 63, 64, 139)]):
+        for a, b in spans:
+            ctx = SimpleNamespace(one_token_each=(b - a == 1), scratch={}, lens=[b - a], starts=[a], max_context=b, dtype=dt)
+            pos, row = torch.arange(a, b, dtype=torch.int32).cuda(), torch.zeros(b - a, dtype=torch.int32).cuda()
+            o = kernels.attention(q[a:b].reshape(b - a, H * D).to(dt).cuda().contiguous(), H * D, H, G, D, kp, vp, table, pages, pos, row, 1, 0.3, ctx)
+            want = v[a:b].repeat_interleave(H // G, dim=1)
+            assert (o.float().cpu().view(b - a, H, D) - want).abs().max() < 1e-2
+
+
 # ------------------------------------------------------------------ norms with gates, sums of branches, the stream
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_gated_norm_kernel(dtype):
+@pytest.mark.parametrize("T,H,Dv,off", [(9, 3, 40, 7), (9, 3, 40, 8), (5, 6, 128, 0), (3, 1, 4100, 4), (4, 5, 6, 3)])
+def test_gated_norm_kernel(dtype, T, H, Dv, off):
+    """Norm over all heads, per head and no norm, times the gate: rows that are and are not aligned for vector accesses, runs that
+    a warp, a block with registers, and a block with a loop take."""
     from pico_engine.ops import kernels
     dt = DTYPES[dtype]
     g = torch.Generator().manual_seed(1)
-    T, H, Dv = 9, 3, 40
     o = torch.randn(T, H * Dv, generator=g) * 3
-    gate = torch.randn(T, 7 + H * Dv, generator=g).to(dt)
+    gate = torch.randn(T, off + H * Dv, generator=g).to(dt)
     tol = 2e-6 if dtype == "float32" else 1e-2
     for group, act, fn in ((H * Dv, "sigmoid", plain.sigmoid), (Dv, "silu", plain.silu), (0, "sigmoid", plain.sigmoid)):
         w = (1 + 0.2 * torch.randn(max(group, 1), generator=g)).to(dt)
         src = o if group else o.to(dt)
-        got = kernels.gated_norm(src.cuda(), group, w.cuda() if group else None, 1e-5, gate.cuda(), 7, act, dt).float().cpu()
+        got = kernels.gated_norm(src.cuda(), group, w.cuda() if group else None, 1e-5, gate.cuda(), off, act, dt).float().cpu()
         x = src.double()
         if group:
             x = plain.norm_plain(x.view(T, -1, group), w.double(), 1e-5).reshape(T, H * Dv)
-        want = x * fn(gate[:, 7:].double())
+        want = x * fn(gate[:, off:].double())
         assert (got - want).abs().max() < tol * max(1.0, float(want.abs().max()))
+        if group:                                           # and without a gate
+            got = kernels.gated_norm(src.cuda(), group, w.cuda(), 1e-5, None, 0, "none", dt).float().cpu()
+            assert (got - x).abs().max() < tol * max(1.0, float(x.abs().max()))
 
 
 @pytest.mark.parametrize("T,W", [(11, 50), (5, 72), (3, 1100)])          # widths that are and are not multiples of 4, below and above 1024
