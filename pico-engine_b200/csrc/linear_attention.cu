@@ -10,7 +10,7 @@
 // area (`state` points at element 0 of slot 0, slots `state_stride` floats apart, [H, D, Dv] row-major) and is
 // zero for a new sequence.
 //
-// A block owns 32 columns of one head's S: thread (ds, j) keeps R consecutive rows of column j in registers,
+// A block owns 32 (or 64) columns of one head's S: thread (ds, j) keeps R consecutive rows of column j (and of j + 32) in registers,
 // so the state is read and written with coalesced accesses and never leaves the registers in between.  Tokens
 // are taken in groups of LA_GROUP: the group's q, k, a and v go to shared memory (vector reads from there), every
 // thread walks the group's tokens, and the LA_DS partial sums of an output are added after the group.
@@ -86,21 +86,24 @@ __device__ __forceinline__ void la_find_chunk(const int* row_first, const int* r
 }
 
 // MODE 0: a sequence's tokens from its stored state; 1: a chunk from zero, leaving (A, L); 2: a chunk from its S_in.
-template <typename T, typename TZ, int R, bool PER_CHANNEL, int MODE>
+// NC: columns of the state a thread keeps (j and j + 32): with two, a block owns 64 columns, and every q, k and decay entry read
+// from shared memory meets two columns' multiply-adds.
+template <typename T, typename TZ, int R, int NC, bool PER_CHANNEL, int MODE>
 __global__ void __launch_bounds__(LA_THREADS) la_walk_kernel(LAArgs a) {
     pdl_launch_dependents();
     pdl_wait();
     constexpr int DP = R * LA_DS;                       // rows the block's threads cover (D rounded up)
+    constexpr int COLS = LA_COLS * NC;                  // columns the block owns
     constexpr bool FAST = sizeof(T) == 2;
     __shared__ __align__(16) float sq[LA_GROUP][DP];
     __shared__ __align__(16) float sk[LA_GROUP][DP];
     __shared__ __align__(16) float sa[PER_CHANNEL ? LA_GROUP : 1][PER_CHANNEL ? DP : 4];
-    __shared__ float sv[LA_GROUP][LA_COLS];
-    __shared__ float part[LA_GROUP][LA_DS][LA_COLS];
+    __shared__ float sv[LA_GROUP][COLS];
+    __shared__ float part[LA_GROUP][LA_DS][COLS];
     __shared__ int where[3];
 
     const int tid = threadIdx.x, jl = tid & (LA_COLS - 1), ds = tid / LA_COLS;
-    const int h = blockIdx.y, j = blockIdx.z * LA_COLS + jl;
+    const int h = blockIdx.y, j0 = blockIdx.z * COLS + jl;
     const int D = a.D, Dv = a.Dv, H = a.H;
     int row, first, count;
     if (MODE == 0) {
@@ -111,15 +114,17 @@ __global__ void __launch_bounds__(LA_THREADS) la_walk_kernel(LAArgs a) {
         row = where[0]; first = where[1]; count = where[2];
     }
     if (count <= 0) return;
-    const bool live = j < Dv;
     const int d0 = ds * R;
 
-    float S[R];
+    float S[NC][R];
     float* sp = nullptr;
     if (MODE == 0) sp = a.state + (size_t)a.slots[row] * a.state_stride + (size_t)h * D * Dv;
     if (MODE == 2) sp = a.chunk_state + ((size_t)blockIdx.x * H + h) * D * Dv;
 #pragma unroll
-    for (int r = 0; r < R; ++r) S[r] = (MODE != 1 && live && d0 + r < D) ? sp[(size_t)(d0 + r) * Dv + j] : 0.f;
+    for (int c = 0; c < NC; ++c)
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+            S[c][r] = (MODE != 1 && j0 + c * LA_COLS < Dv && d0 + r < D) ? sp[(size_t)(d0 + r) * Dv + j0 + c * LA_COLS] : 0.f;
 
     const float hd = PER_CHANNEL ? 0.f : a.head_decay[h];
     float A = 1.f;                                       // MODE 1: the product of this chunk's decays on channel tid
@@ -129,7 +134,7 @@ __global__ void __launch_bounds__(LA_THREADS) la_walk_kernel(LAArgs a) {
     // A group's q, k, a and v are fetched into registers while the group before it is walked, and go to shared memory
     // (activations, scale and the decay's exponentials applied on the way) when that group is done.
     constexpr int NQ = LA_GROUP * DP / LA_THREADS;       // entries of q (and of k, of a) a thread fetches for a group
-    float fq[NQ], fk[NQ], fa[PER_CHANNEL ? NQ : 1], fv = 0.f;
+    float fq[NQ], fk[NQ], fa[PER_CHANNEL ? NQ : 1], fv[NC];
     auto fetch = [&](int g0) {
         const int ng = min(LA_GROUP, count - g0);
 #pragma unroll
@@ -141,8 +146,11 @@ __global__ void __launch_bounds__(LA_THREADS) la_walk_kernel(LAArgs a) {
             fk[n] = on ? to_f(proj[t * a.ld + a.k_off + h * D + d]) : 0.f;
             if constexpr (PER_CHANNEL) fa[n] = on ? to_f(zp[t * a.z_ld + h * D + d]) : 0.f;
         }
-        const int tb = tid / LA_COLS, c = blockIdx.z * LA_COLS + jl;
-        fv = (tb < ng && c < Dv) ? to_f(proj[(size_t)(first + g0 + tb) * a.ld + a.v_off + h * Dv + c]) : 0.f;
+#pragma unroll
+        for (int c = 0; c < NC; ++c) {                   // LA_GROUP * COLS values of v, LA_THREADS a turn
+            const int i = tid + c * LA_THREADS, tb = i / COLS, col = blockIdx.z * COLS + i % COLS;
+            fv[c] = (tb < ng && col < Dv) ? to_f(proj[(size_t)(first + g0 + tb) * a.ld + a.v_off + h * Dv + col]) : 0.f;
+        }
     };
     fetch(0);
     for (int g0 = 0; g0 < count; g0 += LA_GROUP) {
@@ -156,32 +164,42 @@ __global__ void __launch_bounds__(LA_THREADS) la_walk_kernel(LAArgs a) {
             sk[tb][d] = on ? la_act<FAST>(fk[n], a.act_qk) : 0.f;
             if constexpr (PER_CHANNEL) sa[tb][d] = on ? la_channel_decay(fa[n], a.inv_tau) : 0.f;
         }
-        sv[tid / LA_COLS][jl] = la_act<FAST>(fv, a.act_v);
+#pragma unroll
+        for (int c = 0; c < NC; ++c) {
+            const int i = tid + c * LA_THREADS;
+            sv[i / COLS][i % COLS] = la_act<FAST>(fv[c], a.act_v);
+        }
         __syncthreads();
         if (g0 + LA_GROUP < count) fetch(g0 + LA_GROUP);
         if (MODE == 1 && tid < D) {
             for (int tb = 0; tb < ng; ++tb) { if constexpr (PER_CHANNEL) A *= sa[tb][tid]; else A *= hd; }
         }
         auto token = [&](const int tb) {
-            const float v = sv[tb][jl];
-            float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;          // four chains, so that no sum waits for the one before it
+            float v[NC], acc[NC][2];
+#pragma unroll
+            for (int c = 0; c < NC; ++c) { v[c] = sv[tb][c * LA_COLS + jl]; acc[c][0] = 0.f; acc[c][1] = 0.f; }
 #pragma unroll
             for (int r = 0; r < R; r += 4) {
                 const float4 q4 = *reinterpret_cast<const float4*>(&sq[tb][d0 + r]);
                 const float4 k4 = *reinterpret_cast<const float4*>(&sk[tb][d0 + r]);
                 float4 a4 = make_float4(hd, hd, hd, hd);
                 if constexpr (PER_CHANNEL) a4 = *reinterpret_cast<const float4*>(&sa[tb][d0 + r]);
-                S[r + 0] = fmaf(a4.x, S[r + 0], k4.x * v);
-                S[r + 1] = fmaf(a4.y, S[r + 1], k4.y * v);
-                S[r + 2] = fmaf(a4.z, S[r + 2], k4.z * v);
-                S[r + 3] = fmaf(a4.w, S[r + 3], k4.w * v);
-                if (MODE != 1) {
-                    acc0 = fmaf(S[r + 0], q4.x, acc0); acc1 = fmaf(S[r + 1], q4.y, acc1);
-                    acc2 = fmaf(S[r + 2], q4.z, acc2); acc3 = fmaf(S[r + 3], q4.w, acc3);
+#pragma unroll
+                for (int c = 0; c < NC; ++c) {
+                    S[c][r + 0] = fmaf(a4.x, S[c][r + 0], k4.x * v[c]);
+                    S[c][r + 1] = fmaf(a4.y, S[c][r + 1], k4.y * v[c]);
+                    S[c][r + 2] = fmaf(a4.z, S[c][r + 2], k4.z * v[c]);
+                    S[c][r + 3] = fmaf(a4.w, S[c][r + 3], k4.w * v[c]);
+                    if (MODE != 1) {                     // two chains a column, so that no sum waits long for the one before it
+                        acc[c][0] = fmaf(S[c][r + 0], q4.x, acc[c][0]); acc[c][1] = fmaf(S[c][r + 1], q4.y, acc[c][1]);
+                        acc[c][0] = fmaf(S[c][r + 2], q4.z, acc[c][0]); acc[c][1] = fmaf(S[c][r + 3], q4.w, acc[c][1]);
+                    }
                 }
             }
-            const float acc = (acc0 + acc1) + (acc2 + acc3);
-            if (MODE != 1) part[tb][ds][jl] = acc;
+            if (MODE != 1) {
+#pragma unroll
+                for (int c = 0; c < NC; ++c) part[tb][ds][c * LA_COLS + jl] = acc[c][0] + acc[c][1];
+            }
         };
         if (ng == LA_GROUP) {                            // a full group: constant addresses, no loop
 #pragma unroll
@@ -191,20 +209,25 @@ __global__ void __launch_bounds__(LA_THREADS) la_walk_kernel(LAArgs a) {
         }
         if (MODE != 1) {
             __syncthreads();
-            const int tb = tid / LA_COLS, c = blockIdx.z * LA_COLS + jl;       // LA_THREADS = LA_GROUP * LA_COLS outputs a group
-            if (tb < ng && c < Dv) {
-                float o = 0.f;
 #pragma unroll
-                for (int s = 0; s < LA_DS; ++s) o += part[tb][s][jl];
-                a.out[(size_t)(first + g0 + tb) * ((size_t)H * Dv) + (size_t)h * Dv + c] = o;
+            for (int c = 0; c < NC; ++c) {               // LA_GROUP * COLS outputs a group, LA_THREADS a turn
+                const int i = tid + c * LA_THREADS, tb = i / COLS, col = blockIdx.z * COLS + i % COLS;
+                if (tb < ng && col < Dv) {
+                    float o = 0.f;
+#pragma unroll
+                    for (int s = 0; s < LA_DS; ++s) o += part[tb][s][i % COLS];
+                    a.out[(size_t)(first + g0 + tb) * ((size_t)H * Dv) + (size_t)h * Dv + col] = o;
+                }
             }
         }
     }
     if (MODE == 0 || MODE == 1) {
         float* dst = MODE == 0 ? sp : a.chunk_state + ((size_t)blockIdx.x * H + h) * D * Dv;
 #pragma unroll
-        for (int r = 0; r < R; ++r)
-            if (live && d0 + r < D) dst[(size_t)(d0 + r) * Dv + j] = S[r];
+        for (int c = 0; c < NC; ++c)
+#pragma unroll
+            for (int r = 0; r < R; ++r)
+                if (j0 + c * LA_COLS < Dv && d0 + r < D) dst[(size_t)(d0 + r) * Dv + j0 + c * LA_COLS] = S[c][r];
         if (MODE == 1 && blockIdx.z == 0 && tid < D) a.chunk_decay[((size_t)blockIdx.x * H + h) * D + tid] = A;
     }
 }
@@ -233,29 +256,31 @@ __global__ void __launch_bounds__(256) la_carry_kernel(LAArgs a) {
     *sp = carry;
 }
 
-template <typename T, typename TZ, int R, bool PC>
+template <typename T, typename TZ, int R, int NC, bool PC>
 static int la_run(const LAArgs& a, int chunked, cudaStream_t s) {
-    const int tiles = (a.Dv + LA_COLS - 1) / LA_COLS;
+    const int tiles = (a.Dv + LA_COLS * NC - 1) / (LA_COLS * NC);
     if (!chunked) {
-        PE_TRY(pe_launch(la_walk_kernel<T, TZ, R, PC, 0>, dim3(a.B, a.H, tiles), LA_THREADS, 0, s, a));
+        PE_TRY(pe_launch(la_walk_kernel<T, TZ, R, NC, PC, 0>, dim3(a.B, a.H, tiles), LA_THREADS, 0, s, a));
         PE_LAUNCH_CHECK();
         return 0;
     }
-    PE_TRY(pe_launch(la_walk_kernel<T, TZ, R, PC, 1>, dim3(a.max_chunks, a.H, tiles), LA_THREADS, 0, s, a));
+    PE_TRY(pe_launch(la_walk_kernel<T, TZ, R, NC, PC, 1>, dim3(a.max_chunks, a.H, tiles), LA_THREADS, 0, s, a));
     PE_LAUNCH_CHECK();
     const size_t per = (size_t)a.H * a.D * a.Dv;
     PE_TRY(pe_launch(la_carry_kernel, dim3((unsigned)((per + 255) / 256), a.B), 256, 0, s, a));
     PE_LAUNCH_CHECK();
-    PE_TRY(pe_launch(la_walk_kernel<T, TZ, R, PC, 2>, dim3(a.max_chunks, a.H, tiles), LA_THREADS, 0, s, a));
+    PE_TRY(pe_launch(la_walk_kernel<T, TZ, R, NC, PC, 2>, dim3(a.max_chunks, a.H, tiles), LA_THREADS, 0, s, a));
     PE_LAUNCH_CHECK();
     return 0;
 }
 
+// Two columns a thread where the state is at least 64 columns wide and a thread's rows leave the registers for it.
 template <typename T, typename TZ, bool PC>
 static int la_by_rows(const LAArgs& a, int chunked, cudaStream_t s) {
-    if (a.D <= 8 * LA_DS) return la_run<T, TZ, 8, PC>(a, chunked, s);
-    if (a.D <= 16 * LA_DS) return la_run<T, TZ, 16, PC>(a, chunked, s);
-    if (a.D <= 32 * LA_DS) return la_run<T, TZ, 32, PC>(a, chunked, s);
+    const bool two = a.Dv >= 64;
+    if (a.D <= 8 * LA_DS) return two ? la_run<T, TZ, 8, 2, PC>(a, chunked, s) : la_run<T, TZ, 8, 1, PC>(a, chunked, s);
+    if (a.D <= 16 * LA_DS) return two ? la_run<T, TZ, 16, 2, PC>(a, chunked, s) : la_run<T, TZ, 16, 1, PC>(a, chunked, s);
+    if (a.D <= 32 * LA_DS) return la_run<T, TZ, 32, 1, PC>(a, chunked, s);
     return PE_ERR_UNSUPPORTED;
 }
 
