@@ -518,15 +518,52 @@ __global__ void __launch_bounds__(128) moe_route_stream_kernel(const float* x, c
     pdl_wait();
     if (t >= T) return;
     const float* row = x + (size_t)t * K;
+    const int n = E + extra;
+    // VEC (K a multiple of 4, a float32 norm weight, aligned rows): 16-byte reads, four of a lane's reads of the row in flight
+    // at once for the sum of squares (a warp has the row to itself: nothing else hides the latency of its first touch).
+    const bool vec = K % 4 == 0 && nw_dtype == PE_F32 && !(((uintptr_t)x | (uintptr_t)router | (uintptr_t)norm_w) & 15);
     float ss = 0.f;
-    for (int k = lane; k < K; k += 32) ss = fmaf(row[k], row[k], ss);
+    if (vec) {
+        const float4* row4 = reinterpret_cast<const float4*>(row);
+#pragma unroll 4
+        for (int k = lane; k < K / 4; k += 32) { const float4 v = row4[k]; ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w; }
+    } else {
+        for (int k = lane; k < K; k += 32) ss = fmaf(row[k], row[k], ss);
+    }
     const float rstd = 1.0f / sqrtf(warp_sum(ss) / (float)K + eps);
-    for (int e = 0; e < E + extra; ++e) {
-        const float* w = router + (size_t)e * K;
-        float acc = 0.f;
-        for (int k = lane; k < K; k += 32) acc = fmaf(row[k] * load_as_f(norm_w, nw_dtype, k), w[k], acc);
-        acc = warp_sum(acc);
-        if (lane == 0) z[warp][e] = acc * rstd;
+    for (int e0 = 0; e0 < n; e0 += 8) {                                     // eight logits at a time: the row is read once for them
+        float acc[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) acc[u] = 0.f;
+        if (vec) {
+            const float4* row4 = reinterpret_cast<const float4*>(row);
+            const float4* nw4 = reinterpret_cast<const float4*>(norm_w);
+            const float4* r4 = reinterpret_cast<const float4*>(router);
+            for (int k = lane; k < K / 4; k += 32) {
+                float4 xv = row4[k];
+                const float4 w = nw4[k];
+                xv.x *= w.x; xv.y *= w.y; xv.z *= w.z; xv.w *= w.w;
+#pragma unroll
+                for (int u = 0; u < 8; ++u)
+                    if (e0 + u < n) {
+                        const float4 r = r4[(size_t)(e0 + u) * (K / 4) + k];
+                        acc[u] = fmaf(xv.x, r.x, acc[u]); acc[u] = fmaf(xv.y, r.y, acc[u]);
+                        acc[u] = fmaf(xv.z, r.z, acc[u]); acc[u] = fmaf(xv.w, r.w, acc[u]);
+                    }
+            }
+        } else {
+            for (int k = lane; k < K; k += 32) {
+                const float xv = row[k] * load_as_f(norm_w, nw_dtype, k);
+#pragma unroll
+                for (int u = 0; u < 8; ++u)
+                    if (e0 + u < n) acc[u] = fmaf(xv, router[(size_t)(e0 + u) * K + k], acc[u]);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const float sum = warp_sum(acc[u]);
+            if (lane == 0 && e0 + u < n) z[warp][e0 + u] = sum * rstd;
+        }
     }
     __syncwarp();
     moe_choose(z[warp], E, top, extra, weights + (size_t)t * (E + extra), ids ? ids + (size_t)t * top : nullptr, lane);

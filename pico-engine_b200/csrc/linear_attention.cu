@@ -247,11 +247,23 @@ __global__ void __launch_bounds__(256) la_carry_kernel(LAArgs a) {
     const size_t hd = e / a.Dv;                                              // (head, channel)
     float* sp = a.state + (size_t)a.slots[b] * a.state_stride + e;
     float carry = *sp;
-    for (int c = base; c < base + nc; ++c) {
-        float* cs = a.chunk_state + (size_t)c * per + e;
-        const float own = *cs;
-        *cs = carry;
-        carry = fmaf(a.chunk_decay[(size_t)c * a.H * a.D + hd], carry, own);
+    // Eight chunks' contributions and decays are read at once (they do not depend on the carry): one read in flight a thread
+    // would leave the memory system idle, a chunk's data being a megabyte away from the next one's.
+    for (int c0 = base; c0 < base + nc; c0 += 8) {
+        float own[8], dec[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const bool on = c0 + u < base + nc;
+            own[u] = on ? a.chunk_state[(size_t)(c0 + u) * per + e] : 0.f;
+            dec[u] = on ? a.chunk_decay[(size_t)(c0 + u) * a.H * a.D + hd] : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            if (c0 + u < base + nc) {
+                a.chunk_state[(size_t)(c0 + u) * per + e] = carry;
+                carry = fmaf(dec[u], carry, own[u]);
+            }
+        }
     }
     *sp = carry;
 }
