@@ -169,8 +169,9 @@ def kevelorn_kernel_times(eng, size: str, tokens: int, batch: int, context: int,
     gum = torch.randn(tokens, 2 * I, device="cuda").to(bf)
     logits = torch.randn(tokens, moe.spec.n_experts + 1, device="cuda")
     wts = kernels.moe_route(logits, moe.spec.n_experts, moe.spec.top_k, True)
-    entry("prefill choice of experts", device_us(lambda: kernels.moe_route(logits, moe.spec.n_experts, moe.spec.top_k, True)),
-          nbytes=tokens * (moe.spec.n_experts + 1) * 8)
+    norm2 = eng.model.layers[sched[e_gla].layer].feed_forward_norm
+    entry("prefill norm + router + choice of experts", device_us(lambda: kernels.moe_route_stream(
+        x, norm2.weight, norm2.eps, moe.w_router, moe.spec.n_experts, moe.spec.top_k, True)), nbytes=tokens * (W * 4 + (moe.spec.n_experts + 1) * 4))
     entry("prefill silu(gate) x up x expert weight", device_us(lambda: kernels.gated_act(gum, "silu", wts, moe.spec.intermediate)), nbytes=tokens * I * 2 * 3)
     eng.cache.close(slot)
     slots, ctx = _decode_context(eng, batch, context)
