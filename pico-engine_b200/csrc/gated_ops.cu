@@ -506,31 +506,35 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* logits, int
 }
 
 // The same from the float32 residual stream: the logits are router[e] . (x * rsqrt(mean(x^2) + eps) * norm_w), formed in float32
-// by the token's warp (the RMS norm in front of the router is part of this kernel), for up to MR_MAX_E experts (+ the extra row).
+// by the token's block (the RMS norm in front of the router is part of this kernel), for up to MR_MAX_E experts (+ the extra row).
 #define MR_MAX_E 256
-__global__ void __launch_bounds__(128) moe_route_stream_kernel(const float* x, const void* norm_w, int nw_dtype, float eps,
-                                                               const float* router, int K, int E, int top, int extra,
-                                                               float* weights, int* ids, int T) {
+#define MR_THREADS 128
+// A block a token: its four warps share the row (each a quarter of the 16-byte units, so four times the reads are in flight),
+// their partial sums meet in shared memory in a fixed order, and the first warp chooses.
+__global__ void __launch_bounds__(MR_THREADS) moe_route_stream_kernel(const float* x, const void* norm_w, int nw_dtype, float eps,
+                                                                      const float* router, int K, int E, int top, int extra,
+                                                                      float* weights, int* ids, int T) {
     pdl_launch_dependents();
-    __shared__ float z[4][MR_MAX_E + 1];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t = blockIdx.x * 4 + warp;
+    __shared__ float z[MR_MAX_E + 1];
+    __shared__ float part[MR_THREADS / 32][8];
+    __shared__ float red[33];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int t = blockIdx.x;
     pdl_wait();
-    if (t >= T) return;
     const float* row = x + (size_t)t * K;
     const int n = E + extra;
-    // VEC (K a multiple of 4, a float32 norm weight, aligned rows): 16-byte reads, four of a lane's reads of the row in flight
-    // at once for the sum of squares (a warp has the row to itself: nothing else hides the latency of its first touch).
+    // VEC (K a multiple of 4, a float32 norm weight, aligned rows): 16-byte reads, four of a thread's reads of the row in flight
+    // at once for the sum of squares.
     const bool vec = K % 4 == 0 && nw_dtype == PE_F32 && !(((uintptr_t)x | (uintptr_t)router | (uintptr_t)norm_w) & 15);
     float ss = 0.f;
     if (vec) {
         const float4* row4 = reinterpret_cast<const float4*>(row);
 #pragma unroll 4
-        for (int k = lane; k < K / 4; k += 32) { const float4 v = row4[k]; ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w; }
+        for (int k = tid; k < K / 4; k += MR_THREADS) { const float4 v = row4[k]; ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w; }
     } else {
-        for (int k = lane; k < K; k += 32) ss = fmaf(row[k], row[k], ss);
+        for (int k = tid; k < K; k += MR_THREADS) ss = fmaf(row[k], row[k], ss);
     }
-    const float rstd = 1.0f / sqrtf(warp_sum(ss) / (float)K + eps);
+    const float rstd = 1.0f / sqrtf(block_sum(ss, red) / (float)K + eps);
     for (int e0 = 0; e0 < n; e0 += 8) {                                     // eight logits at a time: the row is read once for them
         float acc[8];
 #pragma unroll
@@ -539,7 +543,7 @@ __global__ void __launch_bounds__(128) moe_route_stream_kernel(const float* x, c
             const float4* row4 = reinterpret_cast<const float4*>(row);
             const float4* nw4 = reinterpret_cast<const float4*>(norm_w);
             const float4* r4 = reinterpret_cast<const float4*>(router);
-            for (int k = lane; k < K / 4; k += 32) {
+            for (int k = tid; k < K / 4; k += MR_THREADS) {
                 float4 xv = row4[k];
                 const float4 w = nw4[k];
                 xv.x *= w.x; xv.y *= w.y; xv.z *= w.z; xv.w *= w.w;
@@ -552,28 +556,31 @@ __global__ void __launch_bounds__(128) moe_route_stream_kernel(const float* x, c
                     }
             }
         } else {
-            for (int k = lane; k < K; k += 32) {
+            for (int k = tid; k < K; k += MR_THREADS) {
                 const float xv = row[k] * load_as_f(norm_w, nw_dtype, k);
 #pragma unroll
                 for (int u = 0; u < 8; ++u)
                     if (e0 + u < n) acc[u] = fmaf(xv, router[(size_t)(e0 + u) * K + k], acc[u]);
             }
         }
+        __syncthreads();                                                    // the sums of the eight logits before these have been read
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
             const float sum = warp_sum(acc[u]);
-            if (lane == 0 && e0 + u < n) z[warp][e0 + u] = sum * rstd;
+            if (lane == 0) part[warp][u] = sum;
         }
+        __syncthreads();
+        if (tid < 8 && e0 + tid < n) z[e0 + tid] = ((part[0][tid] + part[1][tid]) + (part[2][tid] + part[3][tid])) * rstd;
     }
-    __syncwarp();
-    moe_choose(z[warp], E, top, extra, weights + (size_t)t * (E + extra), ids ? ids + (size_t)t * top : nullptr, lane);
+    __syncthreads();
+    if (warp == 0) moe_choose(z, E, top, extra, weights + (size_t)t * (E + extra), ids ? ids + (size_t)t * top : nullptr, lane);
 }
 
 extern "C" int pe_moe_route_stream(const float* x, const void* norm_w, int nw_dtype, float eps, const float* router, int K, int E,
                                    int top, int extra, float* weights, int* ids, int T, void* stream) {
     if (T <= 0) return 0;
     if (E <= 0 || E > MR_MAX_E || top <= 0 || top > E || K <= 0) return PE_ERR_UNSUPPORTED;
-    PE_TRY(pe_launch(moe_route_stream_kernel, (T + 3) / 4, 128, 0, (cudaStream_t)stream, x, norm_w, nw_dtype, eps, router, K, E, top, extra,
+    PE_TRY(pe_launch(moe_route_stream_kernel, T, MR_THREADS, 0, (cudaStream_t)stream, x, norm_w, nw_dtype, eps, router, K, E, top, extra,
                      weights, ids, T));
     PE_LAUNCH_CHECK();
     return 0;
