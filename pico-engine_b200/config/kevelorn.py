@@ -51,8 +51,8 @@ def _number(d: dict, key: str, where: str) -> float:
 def _lightning(m: dict, where: str) -> dict:
     heads = _int(m, "heads", where)
     decay = m.get("decay")
-    if not isinstance(decay, list) or len(decay) != heads or not all(isinstance(a, (int, float)) and 0 < a <= 1 for a in decay):
-        raise ConfigError(f"{where}decay must list one number in (0, 1] for each of the {heads} heads, found {decay!r}")
+    if not isinstance(decay, list) or len(decay) != heads or not all(isinstance(a, (int, float)) and not isinstance(a, bool) and a >= 0 for a in decay):
+        raise ConfigError(f"{where}decay must list one number (not negative) for each of the {heads} heads, found {decay!r}")
     return {"heads": heads, "dim": _int(m, "dim", where), "vdim": _int(m, "vdim", where), "decay": [float(a) for a in decay]}
 
 

@@ -211,7 +211,8 @@ def plain_recurrence(q, k, v, lens, decay):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("H,D,Dv", [(2, 16, 8), (3, 24, 40), (1, 64, 64), (2, 136, 12), (4, 128, 33), (1, 200, 96)])
+@pytest.mark.parametrize("H,D,Dv", [(2, 16, 8), (3, 24, 40), (1, 64, 64), (2, 136, 12), (4, 128, 33), (1, 200, 96), (2, 128, 128), (1, 96, 72),
+                                    (3, 40, 100)])
 def test_recurrence_kernel_fixed_decay(dtype, H, D, Dv):
     """Sequences whose lengths fall on, before and after chunk borders, as one prompt step (chunked and token after token),
     in portions, and with the last tokens one by one; the states are compared too."""
@@ -230,7 +231,7 @@ def test_recurrence_kernel_fixed_decay(dtype, H, D, Dv):
         assert (s.double() - want_s).abs().max() < tol * 10, (cuts, chunked)
 
 
-@pytest.mark.parametrize("H,D,Dv,tau", [(2, 16, 8, 1.0), (3, 48, 32, 16.0), (1, 136, 24, 4.0)])
+@pytest.mark.parametrize("H,D,Dv,tau", [(2, 16, 8, 1.0), (3, 48, 32, 16.0), (1, 136, 24, 4.0), (2, 80, 64, 8.0), (1, 128, 160, 2.0)])
 def test_recurrence_kernel_decay_per_channel(H, D, Dv, tau):
     """A learned decay per key channel and token, query scale and silu on the projections."""
     g = torch.Generator().manual_seed(D)
