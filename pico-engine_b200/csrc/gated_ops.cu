@@ -75,6 +75,63 @@ __global__ void __launch_bounds__(256) rotary_norm_store_kernel(T* qkv, int ld, 
     }
 }
 
+// bfloat16 with even D, Dv and ld: a lane takes whole pairs (4-byte accesses), so a pair is rotated inside one lane.
+template <int NP>
+__global__ void __launch_bounds__(256) rotary_norm_store_pairs_kernel(bf16* qkv, int ld, int H, int G, int D, int Dv, const float* freq,
+                                                                      int rot_dims, int norm, float eps, const int* tok_pos,
+                                                                      const int* tok_row, bf16* k_pool, bf16* v_pool, const int* table,
+                                                                      int table_stride, int store) {
+    pdl_launch_dependents();
+    __shared__ float s_cos[128], s_sin[128];
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    pdl_wait();
+    bf16* row = qkv + (size_t)t * ld;
+    const int pos = tok_pos[t];
+    for (int i = threadIdx.x; i < rot_dims / 2; i += blockDim.x) sincosf((float)pos * freq[i], &s_sin[i], &s_cos[i]);
+    long long page = -1;
+    if (store) page = table[(size_t)tok_row[t] * table_stride + pos / PE_PAGE];
+    __syncthreads();
+    const int pairs = D / 2;
+    for (int u = warp; u < H + 2 * G; u += (int)(blockDim.x >> 5)) {
+        if (u < H + G) {
+            __nv_bfloat162* v = reinterpret_cast<__nv_bfloat162*>(row + (size_t)u * D);
+            float2 val[NP];
+            float ss = 0.f;
+#pragma unroll
+            for (int e = 0; e < NP; ++e) {
+                const int i = lane + 32 * e;
+                float2 f = make_float2(0.f, 0.f);
+                if (i < pairs) {
+                    f = __bfloat1622float2(v[i]);
+                    if (2 * i + 1 < rot_dims) {
+                        const float sn = s_sin[i], cs = s_cos[i];
+                        f = make_float2(fmaf(f.x, cs, -f.y * sn), fmaf(f.y, cs, f.x * sn));
+                    }
+                }
+                val[e] = f;
+                ss += f.x * f.x + f.y * f.y;
+            }
+            const float rstd = norm ? 1.0f / sqrtf(warp_sum(ss) / (float)D + eps) : 1.0f;
+            __nv_bfloat162* dst = (u >= H && store && page >= 0)
+                ? reinterpret_cast<__nv_bfloat162*>(k_pool + (((size_t)page * G + (u - H)) * PE_PAGE + pos % PE_PAGE) * D) : nullptr;
+#pragma unroll
+            for (int e = 0; e < NP; ++e) {
+                const int i = lane + 32 * e;
+                if (i < pairs) {
+                    const __nv_bfloat162 o = __floats2bfloat162_rn(val[e].x * rstd, val[e].y * rstd);
+                    v[i] = o;
+                    if (dst) dst[i] = o;
+                }
+            }
+        } else if (store && page >= 0) {
+            const int c = u - H - G;
+            const __nv_bfloat162* v = reinterpret_cast<const __nv_bfloat162*>(row + (size_t)(H + G) * D + (size_t)c * Dv);
+            __nv_bfloat162* dst = reinterpret_cast<__nv_bfloat162*>(v_pool + (((size_t)page * G + c) * PE_PAGE + pos % PE_PAGE) * Dv);
+            for (int d = lane; d < Dv / 2; d += 32) dst[d] = v[d];
+        }
+    }
+}
+
 extern "C" int pe_rotary_norm_store(void* qkv, int dtype, int ld, int T, int H, int G, int D, int Dv, const float* freq, int rot_dims,
                                     int norm, float eps, const int* tok_pos, const int* tok_row, void* k_pool, void* v_pool,
                                     const int* table, int table_stride, int store, void* stream) {
@@ -82,6 +139,14 @@ extern "C" int pe_rotary_norm_store(void* qkv, int dtype, int ld, int T, int H, 
     if (D > 256 || rot_dims > D || (rot_dims & 1) || (rot_dims > 0 && !freq) || ld < (H + G) * D + G * Dv) return PE_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = H + 2 * G > 16 ? 256 : 128;                        // a warp walks at most about four heads
+    if (dtype == PE_BF16 && D % 2 == 0 && Dv % 2 == 0 && ld % 2 == 0 && !(((uintptr_t)qkv | (uintptr_t)k_pool | (uintptr_t)v_pool) & 3)) {
+#define ROT_PAIRS(NP) PE_TRY(pe_launch(rotary_norm_store_pairs_kernel<NP>, T, threads, 0, s, (bf16*)qkv, ld, H, G, D, Dv, freq, rot_dims, norm, eps, \
+                                       tok_pos, tok_row, (bf16*)k_pool, (bf16*)v_pool, table, table_stride, store))
+        if (D <= 64) ROT_PAIRS(1); else if (D <= 128) ROT_PAIRS(2); else ROT_PAIRS(4);
+#undef ROT_PAIRS
+        PE_LAUNCH_CHECK();
+        return 0;
+    }
 #define ROT_LAUNCH(TT, NE) PE_TRY(pe_launch(rotary_norm_store_kernel<TT, NE>, T, threads, 0, s, (TT*)qkv, ld, H, G, D, Dv, freq, rot_dims, norm, eps, \
                                             tok_pos, tok_row, (TT*)k_pool, (TT*)v_pool, table, table_stride, store))
     if (dtype == PE_F32) {

@@ -264,14 +264,15 @@ def test_recurrence_keeps_a_key_from_far_back(far):
 
 # ------------------------------------------------------------------ rotation, unit norm and the cache write; the window
 
+@pytest.mark.parametrize("pad", [5, 6])          # rows of odd and of even length (the latter let a lane take whole pairs)
 @pytest.mark.parametrize("D", [24, 80, 200])
-def test_rotation_norm_and_store(D):
+def test_rotation_norm_and_store(D, pad):
     from pico_engine.ops import kernels
     H, G, Dv, n = 3, 1, 40, 70
     g = torch.Generator().manual_seed(3)
     for dtype, tol in ((torch.float32, 2e-6), (torch.bfloat16, 1e-2)):
         for dims, norm in ((D, True), (8, True), (0, True), (16, False)):
-            row = torch.randn(n, H * D + G * D + G * Dv + 5, generator=g).to(dtype)
+            row = torch.randn(n, H * D + G * D + G * Dv + pad, generator=g).to(dtype)
             pos = torch.arange(100, 100 + n, dtype=torch.int32)
             freq = (50.0 ** (-2.0 * torch.arange(dims // 2, dtype=torch.float64) / max(dims, 1)) / 3.0).float()
             kp, vp = torch.zeros(4, G, 64, D, dtype=dtype).cuda(), torch.zeros(4, G, 64, Dv, dtype=dtype).cuda()
