@@ -3,7 +3,7 @@
 //   per head:   S_t = diag(a_t) S_(t-1) + k_t v_t^T        o_t = S_t^T q_t        S [D, Dv], float32
 //
 // a_t is either one constant per head (`head_decay` [H]) or one number per key channel and token,
-// a = sigmoid(z)^(inv_tau) = exp(-softplus(-z) * inv_tau) from logits `z` [T, H*D].  q, k and v are columns of
+// a = sigmoid(z)^(inv_tau) = exp(-softplus(-z) * inv_tau) from float32 logits `z` [T, H*D].  q, k and v are columns of
 // `proj` [T, ld] (heads side by side, q_off / k_off / v_off the first column of each); an activation (0: none,
 // 1: silu) is applied to q and k and to v while they are loaded, and q is multiplied by `q_scale`.  Everything
 // after the load is float32; o [T, H*Dv] is written as float32.  A sequence's S lives in its slot of the state
@@ -331,7 +331,6 @@ extern "C" int pe_linear_attention(const void* proj, int dtype, int ld, int q_of
     if (dtype == PE_BF16) {
         if (!pc) return la_by_rows<bf16, bf16, false>(a, chunked, s);
         if (z_dtype == PE_F32) return la_by_rows<bf16, float, true>(a, chunked, s);
-        if (z_dtype == PE_BF16) return la_by_rows<bf16, bf16, true>(a, chunked, s);
     }
     return PE_ERR_UNSUPPORTED;
 }

@@ -914,7 +914,7 @@ def linear_attention(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, n_h
                      v_activation: str = "none") -> torch.Tensor:
     """o [T, H * Dv] float32 of S_t = diag(a_t) S_(t-1) + k_t v_t^T, o_t = S_t^T q_t per head, for q, k, v at columns
     ``q_off``, ``k_off``, ``v_off`` of proj [T, ld] (packed sequences).  The decay is ``head_decay`` [H] float32 (one constant
-    a head) or sigmoid(``decay_logits`` [T, H * D])^``inv_tau`` (a number per key channel and token).  S [H, D, Dv] comes from
+    a head) or sigmoid(``decay_logits`` float32 [T, H * D])^``inv_tau`` (a number per key channel and token).  S [H, D, Dv] comes from
     and returns to the sequences' float32 state at ``state_offset``.  ``chunked``: prompts, three launches over chunks of
     the sequences; else token after token in one launch."""
     T, ld = proj.shape
@@ -927,7 +927,7 @@ def linear_attention(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, n_h
     if head_decay is not None:
         _need(head_decay, "head_decay", torch.float32, (H,))
     else:
-        _need(decay_logits, "decay_logits", None, (T, H * D))
+        _need(decay_logits, "decay_logits", torch.float32, (T, H * D))
     sp, stride = _state_args(state, state_offset, H * D * Dv)
     B = slots.shape[0]
     out = torch.empty(T, H * Dv, dtype=torch.float32, device=proj.device)
